@@ -6,7 +6,7 @@ What the reference does in one PagedAllocator + KVCache for one uniform tensor
 mixers need the same thing (kv heads, head size, window) share a pool of pages and one block
 table per request.  A group with a window gives a page back as soon as every key in it lies
 before the window of the next position.  Storage of a group is
-[steps, 2 (k, v), pages + 1, kv_heads, page_size, head_dim]: one (page, kv head) is a
+[steps, planes (k, v; or one), pages + 1, kv_heads, page_size, head_dim]: one (page, kv head) is a
 contiguous page_size x head_dim tile that a kernel can fetch in one bulk copy.
 
 Call order for a request: admit -> (ensure -> commit)* -> free.
@@ -91,11 +91,11 @@ class CacheManager:
             if allocate:
                 g.device_table = torch.zeros((max_seqs + 1, self.max_pages_per_seq), dtype=torch.int32, device=self.device)
                 n = g.need
-                g.storage = torch.zeros((len(g.steps), 2, num_pages + 1, n.num_kv_heads, page_size, n.head_dim),
+                g.storage = torch.zeros((len(g.steps), n.planes, num_pages + 1, n.num_kv_heads, page_size, n.head_dim),
                                         dtype=dtype, device=self.device)
             for j, step in enumerate(g.steps):
                 k = g.storage[j, 0] if allocate else None
-                v = g.storage[j, 1] if allocate else None
+                v = g.storage[j, 1] if allocate and g.need.planes > 1 else None
                 self.layer_caches[step] = LayerCache(gi, k=k, v=v)
         for g in self.state_groups:
             if allocate:
@@ -111,7 +111,7 @@ class CacheManager:
     def bytes_per_token(self) -> int:
         """Bytes of cache one token occupies over all groups (engine/core/kv_cache.py:22-30)."""
         el = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * len(g.steps) * g.need.num_kv_heads * g.need.head_dim * el for g in self.kv_groups)
+        return sum(g.need.planes * len(g.steps) * g.need.num_kv_heads * g.need.head_dim * el for g in self.kv_groups)
 
     def state_bytes_per_seq(self) -> int:
         """Bytes of fixed-size state one live request occupies over all state groups."""

@@ -33,6 +33,8 @@ def supported_architectures() -> Dict[str, str]:
 def resolve(raw_config: dict) -> Architecture:
     _load_builtin()
     archs = raw_config.get("architectures") or []
+    if not archs and isinstance(raw_config.get("architecture"), str):        # the singular spelling names one class
+        archs = [raw_config["architecture"]]
     if not archs:
         raise ConfigError("config.json has no 'architectures' entry")
     name = archs[0]

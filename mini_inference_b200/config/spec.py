@@ -63,9 +63,13 @@ class LayerSpec:
 class ExecStep:
     """One entry of the execution order.  layer indexes ModelSpec.layers (a layer may be named
     by several steps: shared weights, separate caches).  cache_from names an EARLIER step whose
-    cache this step's mixer reads instead of owning one."""
+    cache this step's mixer reads instead of owning one.  add_row names a row of the model's
+    table of pass vectors (ModelSpec.pass_vectors_name) that is added to the residual stream
+    right before this step's layer runs (a model that repeats a span of layers marks each
+    repetition this way)."""
     layer: int
     cache_from: Optional[int] = None
+    add_row: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -81,6 +85,15 @@ class ModelSpec:
     max_position: int
     eos_token_ids: Tuple[int, ...] = ()
     extra: Tuple[Tuple[str, Any], ...] = field(default=())
+    # a norm applied to the embedded tokens before the first layer (None: the embedding enters the stream as it is)
+    embedding_norm: Optional[PartSpec] = None
+    embedding_norm_name: Optional[str] = None
+    # a [rows, hidden] tensor whose rows ExecStep.add_row names
+    pass_vectors_name: Optional[str] = None
+    pass_vectors_rows: int = 0
+    # "compute": the residual stream has the run's dtype; "float32": it is kept in 32 bits whatever the run's dtype
+    # (the norms of such a model read and write a float32 stream and hand rows of the run's dtype to the parts)
+    residual: str = "compute"
 
     def __post_init__(self):
         for i, step in enumerate(self.order):
@@ -91,3 +104,7 @@ class ModelSpec:
                     raise ValueError(f"order[{i}] reads the cache of step {step.cache_from}, which does not run before it")
                 if self.order[step.cache_from].cache_from is not None:
                     raise ValueError(f"order[{i}] reads the cache of step {step.cache_from}, which owns none")
+            if step.add_row is not None and not 0 <= step.add_row < self.pass_vectors_rows:
+                raise ValueError(f"order[{i}] adds pass vector {step.add_row}; the model has {self.pass_vectors_rows}")
+        if self.residual not in ("compute", "float32"):
+            raise ValueError(f"residual '{self.residual}' is not one of compute, float32")

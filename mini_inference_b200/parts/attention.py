@@ -15,6 +15,19 @@ import torch
 from .base import KVCacheNeed, Part, WeightSpec, register_mixer
 
 
+def paged_attention_step_arrays(facts):
+    """The paged attention kernels' work lists (shared by every mixer whose step_arrays_key is "paged_attention"): the
+    entries that feed one token (decode kernels), and for the longer entries one (entry, first row) pair per tile of
+    query rows (prompt kernels; the tensor-core kernel takes tiles twice as tall)."""
+    lens, tile = facts.lens, facts.tile
+    decode = [i for i, n in enumerate(lens) if n == 1]
+    tiles = [(i, r) for i, n in enumerate(lens) if n > 1 for r in range(0, n, tile)]
+    tiles2 = [(i, r) for i, n in enumerate(lens) if n > 1 for r in range(0, n, 2 * tile)]
+    as_i32 = lambda v, shape: np.asarray(v, dtype=np.int32).reshape(shape)      # noqa: E731
+    return {"decode_segs": as_i32(decode, (-1,)), "prefill_tiles": as_i32(tiles, (-1, 2)),
+            "prefill_tiles2": as_i32(tiles2, (-1, 2))}
+
+
 @register_mixer("gqa_attention")
 class GQAAttention(Part):
     offers_open = True
@@ -60,17 +73,7 @@ class GQAAttention(Part):
     def step_flops(self, rows, pairs):
         return 4 * self.H * self.D * pairs                 # q.k and p.v, a multiply and an add each
 
-    def step_arrays(self, facts):
-        """The attention kernels' work lists: the entries that feed one token (decode kernel), and for the longer
-        entries one (entry, first row) pair per tile of query rows (prompt kernels; the tensor-core kernel takes
-        tiles twice as tall)."""
-        lens, tile = facts.lens, facts.tile
-        decode = [i for i, n in enumerate(lens) if n == 1]
-        tiles = [(i, r) for i, n in enumerate(lens) if n > 1 for r in range(0, n, tile)]
-        tiles2 = [(i, r) for i, n in enumerate(lens) if n > 1 for r in range(0, n, 2 * tile)]
-        as_i32 = lambda v, shape: np.asarray(v, dtype=np.int32).reshape(shape)      # noqa: E731
-        return {"decode_segs": as_i32(decode, (-1,)), "prefill_tiles": as_i32(tiles, (-1, 2)),
-                "prefill_tiles2": as_i32(tiles2, (-1, 2))}
+    step_arrays = staticmethod(paged_attention_step_arrays)
 
     def forward(self, h, ctx, cache, position, owns_cache=True):
         o, w = self.forward_open(h, ctx, cache, position, owns_cache)

@@ -51,6 +51,11 @@ a block reads the attributes, it never probes with hasattr:
                                the start-up timing of many-row kernels then times that instead of the bare product
   accepts_deferred = True  Norm: forward hands `delta` to ctx.ops.add_rmsnorm untouched, so the block may give it the
                                result of ctx.ops.linear(..., defer=True) (possibly partial sums the kernel adds up)
+  keeps_float32_stream = True
+                           Norm: forward takes a float32 stream x (and keeps it float32), returns rows of the run's dtype, and
+                               accepts pre_add=<float32 [hidden]> (a vector added to every row of the stream before the norm);
+                               embed(ids, table, ctx, float32) gathers and norms embedded tokens into a new stream.  A spec
+                               with residual="float32" needs it of all its norms
   takes_next_weight = True Norm: forward accepts next_weight=<tensor> and passes it to ctx.ops.add_rmsnorm: the block
                                names the first weight of the part that follows, and the kernel may request it into L2
 """
@@ -65,7 +70,7 @@ from ..config.spec import PartSpec
 @dataclass(frozen=True)
 class WeightSpec:
     name: str                       # part-local name, e.g. "q_proj"
-    shape: Tuple[int, ...]
+    shape: Tuple[int, ...]          # a size of -1 is taken from the checkpoint (random-weights mode cannot draw such a tensor)
     kind: str = "matrix"            # "matrix" (GEMM operand) | "vector" | "table" (integers)
     init: str = "normal"            # random-weights mode: "normal" | "norm" | "zeros"
     optional: bool = False
@@ -73,10 +78,13 @@ class WeightSpec:
 
 @dataclass(frozen=True)
 class KVCacheNeed:
-    """Keys and values in pages; window=None keeps every key, W keeps the last W."""
+    """Keys and values in pages; window=None keeps every key, W keeps the last W.  planes: 2 = a key and a value
+    pool; 1 = one pool of rows per token (a mixer that caches one compressed vector per token and derives both
+    keys and values from it); the LayerCache then has no v."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    planes: int = 2
 
 
 @dataclass(frozen=True)
@@ -110,6 +118,7 @@ class Part:
     gated_weight = None
     accepts_deferred = False
     takes_next_weight = False
+    keeps_float32_stream = False     # Norm: reads and writes a float32 residual stream whatever the run's dtype, takes pre_add=
     step_arrays_key: Optional[str] = None
 
     def first_product_probe(self, ops, rows):

@@ -19,29 +19,42 @@ class PreNormBlock(Part):
     def __init__(self, spec, parts):
         super().__init__(spec)
         self.parts = dict(parts)
-        self.mixer, self.feed_forward = parts["mixer"], parts["feed_forward"]
-        self.norm1, self.norm2, self.position = parts["norm1"], parts["norm2"], parts["position"]
+        self.mixer, self.feed_forward = parts["mixer"], parts.get("feed_forward")
+        self.norm1, self.norm2, self.position = parts["norm1"], parts.get("norm2"), parts["position"]
         self.open_mixer = bool(self.mixer.offers_open)
-        self.open_ffn = bool(self.feed_forward.offers_open)
+        self.open_ffn = bool(self.feed_forward is not None and self.feed_forward.offers_open)
         self.hint1 = bool(self.norm1.takes_next_weight)
-        self.hint2 = bool(self.norm2.takes_next_weight)
+        self.hint2 = bool(self.norm2 is not None and self.norm2.takes_next_weight)
 
     def norms(self):
-        return [self.norm1, self.norm2]
+        return [n for n in (self.norm1, self.norm2) if n is not None]
 
-    def forward(self, x, delta, ctx, cache, owns_cache=True):
+    def forward(self, x, delta, ctx, cache, owns_cache=True, pre_add=None):
+        """pre_add: a vector added to every row of the stream before this layer (the first norm's kernel adds it
+        together with the pending delta); only norms that declare keeps_float32_stream take it."""
         ops = ctx.ops
         w1 = self.mixer.first_weight if self.hint1 else None
-        h = self.norm1.forward(x, delta, ctx, next_weight=w1) if w1 is not None else self.norm1.forward(x, delta, ctx)
+        if pre_add is not None:
+            h = self.norm1.forward(x, delta, ctx, pre_add=pre_add)
+        else:
+            h = self.norm1.forward(x, delta, ctx, next_weight=w1) if w1 is not None else self.norm1.forward(x, delta, ctx)
         defer = ctx.defer_ok                   # the readers of `a` and of the returned delta are norms that accept it
         if self.open_mixer:
             rows, w_out = self.mixer.forward_open(h, ctx, cache, self.position, owns_cache)
             a = ops.linear(rows, w_out, defer=True) if defer else ops.linear(rows, w_out)
         else:
             a = self.mixer.forward(h, ctx, cache, self.position, owns_cache)
+        if self.feed_forward is None:
+            return x, a
         w2 = self.feed_forward.first_weight if self.hint2 else None
         h = self.norm2.forward(x, a, ctx, next_weight=w2) if w2 is not None else self.norm2.forward(x, a, ctx)
         if self.open_ffn and defer:
             rows, w_out = self.feed_forward.forward_open(h, ctx)
             return x, ops.linear(rows, w_out, defer=True)
         return x, self.feed_forward.forward(h, ctx)
+
+
+@register_block("prenorm_mixer")
+class PreNormMixerOnly(PreNormBlock):
+    """A layer without feed-forward: x = x + mixer(norm1(x))."""
+    roles = {"mixer": "mixer", "norm1": "norm", "position": "position"}

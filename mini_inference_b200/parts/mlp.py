@@ -50,3 +50,34 @@ class SwiGLU(Part):
     def forward_open(self, h, ctx):
         """Everything but the last product: (silu(gate) * up, down weight)."""
         return ctx.ops.gated_linear(h, self.gate_up), self.down
+
+
+@register_feed_forward("polynorm_mlp")
+class PolyNormMLP(Part):
+    """down(act(up(h))) with the polynomial-norm activation
+        act(z) = a N(z) + b N(z^2) + c N(z^3) + e,   N(y) = y / sqrt(mean(y^2) + eps) over a token's row,
+    powers taken element by element; a, b, c, e are the four learned numbers of the tensor `act`.
+    The three statistics are float32 sums over the row, made in one pass by one kernel."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(spec.get("hidden_size"))
+        self.inter = int(spec.get("intermediate_size"))
+        self.eps = float(spec.get("eps"))
+        self.up = self.down = self.coef = None
+
+    def weight_specs(self):
+        return [WeightSpec("up", (self.inter, self.hidden)), WeightSpec("down", (self.hidden, self.inter)),
+                WeightSpec("act", (4,), kind="vector", init="norm")]
+
+    def load(self, tensors, dtype, device):
+        self.up, self.down = tensors.pop("up"), tensors.pop("down")
+        self.coef = tensors.pop("act").float().contiguous()
+
+    @property
+    def first_weight(self):
+        return self.up
+
+    def forward(self, h, ctx):
+        ops = ctx.ops
+        return ops.linear(ops.polynorm(ops.linear(h, self.up), self.coef, self.eps), self.down)

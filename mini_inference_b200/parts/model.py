@@ -43,12 +43,20 @@ class DecoderModel:
                     self._owned.append((names[key], ws, part))
             self.blocks.append(block_cls(PartSpec.of(layer.block), parts))
         self.final_norm = build_part("norm", spec.final_norm)
+        self.embedding_norm = build_part("norm", spec.embedding_norm) if spec.embedding_norm is not None else None
         norms = [p for b in self.blocks for role, p in b.parts.items() if b.roles[role] == "norm"] + [self.final_norm]
+        if self.embedding_norm is not None:
+            norms.append(self.embedding_norm)
+            for ws in self.embedding_norm.weight_specs():
+                self._owned.append((spec.embedding_norm_name, ws, self.embedding_norm))
+        if spec.residual == "float32" and not all(n.keeps_float32_stream for n in norms):
+            raise ValueError("the spec keeps the residual stream in float32, but one of its norms does not offer that")
         self._norms_accept_deferred = all(n.accepts_deferred for n in norms)
         for ws in self.final_norm.weight_specs():
             self._owned.append((spec.final_norm_name, ws, self.final_norm))
         self.embedding = None
         self.lm_head = None
+        self.pass_vectors = None
         self.dtype = None
         self.device = None
 
@@ -57,6 +65,9 @@ class DecoderModel:
         """Every tensor the checkpoint must hold: (checkpoint name, spec)."""
         table = [(self.spec.embedding_name, WeightSpec("embedding", (self.spec.vocab_size, self.spec.hidden_size)))]
         table += [(name, ws) for name, ws, _ in self._owned]
+        if self.spec.pass_vectors_name is not None:
+            table.append((self.spec.pass_vectors_name, WeightSpec("pass_vectors", (self.spec.pass_vectors_rows, self.spec.hidden_size),
+                                                                  kind="vector")))
         if self.spec.lm_head_name is not None:
             table.append((self.spec.lm_head_name, WeightSpec("lm_head", (self.spec.vocab_size, self.spec.hidden_size))))
         return table
@@ -80,6 +91,9 @@ class DecoderModel:
             if id(position) not in seen:
                 position.load({}, dtype, self.device)
         self.embedding = tensors[self.spec.embedding_name]
+        if self.spec.pass_vectors_name is not None:            # added to a float32 stream or to one of the run's dtype
+            pv = tensors[self.spec.pass_vectors_name]
+            self.pass_vectors = (pv.float() if self.spec.residual == "float32" else pv.to(dtype)).contiguous()
         self.lm_head = self.embedding if self.spec.lm_head_name is None else tensors[self.spec.lm_head_name]
 
     def matrix_weights(self):
@@ -160,13 +174,21 @@ class DecoderModel:
         b, ops = ctx.batch, ctx.ops
         ctx.defer_ok = self._norms_accept_deferred and getattr(ops, "deferred", False)
         ctx.hints_ok = getattr(ops, "takes_hints", False)
-        x = ops.embedding(b.token_ids, self.embedding)
+        if self.embedding_norm is not None:                    # gather and norm in one kernel; the stream starts normed
+            x = self.embedding_norm.embed(b.token_ids, self.embedding, ctx, float32=self.spec.residual == "float32")
+        else:
+            x = ops.embedding(b.token_ids, self.embedding)
         for position in self._positions.values():
             x = position.on_embedding(x, ctx)
         delta = None
         for i, step in enumerate(self.spec.order):
             src = i if step.cache_from is None else step.cache_from
-            x, delta = self.blocks[step.layer].forward(x, delta, ctx, caches[src], step.cache_from is None)
+            block = self.blocks[step.layer]
+            if step.add_row is None:
+                x, delta = block.forward(x, delta, ctx, caches[src], step.cache_from is None)
+            else:
+                x, delta = block.forward(x, delta, ctx, caches[src], step.cache_from is None,
+                                         pre_add=self.pass_vectors[step.add_row])
         if b.num_logit_rows == 0:
             return None
         h = self.final_norm.forward(x, delta, ctx, rows=b.logit_rows)

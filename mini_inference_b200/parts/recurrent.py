@@ -1,0 +1,147 @@
+"""Mixers that keep a fixed-size matrix state per request instead of keys and values.
+
+Both keep, per head, a float32 state S [key_dim, value_dim] in the request's state slot and
+walk the tokens of a step's entry in order from the state that earlier steps left; prompt
+portions and single decoded tokens go through the same kernels.  The columns of S never mix
+(every update is "row factors times S plus key times a row vector"), so a kernel gives every
+column to a few lanes that hold its rows in registers.
+
+lightning       q, k, v = silu(W h);  S <- decay_h S + k v^T;  o = S^T q
+                rows: rmsnorm over all heads' outputs together * weight, * sigmoid(W_g h)
+channel_delta   q, k, v = silu(causal_conv(W h)); q, k unit vectors per head (q also * key_dim^-1/2);
+                beta = sigmoid(W_b h); per head and key channel g = exp(-exp(A_log) softplus(W_a2 W_a1 h + dt_bias));
+                S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+                rows: per head o / rms(o) * weight [value_dim], * sigmoid(W_g2 W_g1 h)
+                The last conv_taps - 1 projected inputs are part of the state (behind S in the slot).
+"""
+from __future__ import annotations
+
+import torch
+
+from .base import Part, StateNeed, WeightSpec, register_mixer
+
+
+@register_mixer("lightning")
+class LightningAttention(Part):
+    offers_open = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        g = spec.get
+        self.hidden, self.H, self.D, self.V = int(g("hidden_size")), int(g("num_heads")), int(g("key_dim")), int(g("value_dim"))
+        self.decay_values = tuple(float(v) for v in g("decay"))
+        self.eps = float(g("out_norm_eps"))
+        if len(self.decay_values) != self.H:
+            raise ValueError(f"{len(self.decay_values)} decay constants for {self.H} heads")
+        self.proj = self.o = self.norm = self.decay = None
+
+    def weight_specs(self):
+        H, D, V, hid = self.H, self.D, self.V, self.hidden
+        return [WeightSpec("q", (H * D, hid)), WeightSpec("k", (H * D, hid)), WeightSpec("v", (H * V, hid)),
+                WeightSpec("g", (H * V, hid)), WeightSpec("o", (hid, H * V)),
+                WeightSpec("norm", (H * V,), kind="vector", init="norm")]
+
+    def cache_need(self):
+        return StateNeed((self.H * self.D * self.V,), "float32")
+
+    def load(self, tensors, dtype, device):
+        self.proj = torch.cat([tensors.pop(n) for n in ("q", "k", "v", "g")], dim=0).contiguous()     # one product for all four
+        self.o = tensors.pop("o")
+        self.norm = tensors.pop("norm").float().contiguous()
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=device)
+
+    @property
+    def open_weight(self):
+        return self.o
+
+    @property
+    def first_weight(self):
+        return self.proj
+
+    def step_flops(self, rows, pairs):
+        return 4 * self.H * self.D * self.V * rows                 # state update and read-out, a multiply and an add each
+
+    def forward(self, h, ctx, cache, position, owns_cache=True):
+        rows, w = self.forward_open(h, ctx, cache, position, owns_cache)
+        return ctx.ops.linear(rows, w)
+
+    def forward_open(self, h, ctx, cache, position, owns_cache=True):
+        ops, H, D, V = ctx.ops, self.H, self.D, self.V
+        p = ops.linear(h, self.proj)                                # [T, 2 H D + 2 H V]: q | k | v | gate
+        o = ops.lightning_scan(p, H, D, V, self.decay, cache.state, ctx.batch)          # float32 [T, H V]
+        rows = ops.group_rmsnorm_gate(o, self.norm, p[:, 2 * H * D + H * V:], self.eps, 1, H * V, ctx.dtype)
+        return rows, self.o
+
+
+@register_mixer("channel_delta")
+class ChannelDeltaRule(Part):
+    offers_open = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        g = spec.get
+        self.hidden, self.H, self.KV = int(g("hidden_size")), int(g("num_heads")), int(g("num_kv_heads"))
+        self.D, self.V, self.taps = int(g("key_dim")), int(g("value_dim")), int(g("conv_taps"))
+        self.eps, self.unit_eps = float(g("out_norm_eps")), float(g("unit_eps"))
+        if self.H % self.KV:
+            raise ValueError(f"{self.H} heads are not a multiple of {self.KV} key heads")
+        # the low ranks of the decay and gate projections are the checkpoint's business (-1: any); a configuration
+        # that is to be filled with random weights names them
+        self.a_rank, self.g_rank = int(g("decay_rank", -1)), int(g("gate_rank", -1))
+        self.C = 2 * self.KV * self.D + self.H * self.V             # channels that pass the short convolution
+        self.proj = self.a2 = self.g2 = self.o = self.conv = self.A_log = self.dt_bias = self.norm = None
+
+    def weight_specs(self):
+        H, KV, D, V, hid, taps = self.H, self.KV, self.D, self.V, self.hidden, self.taps
+        return [WeightSpec("q", (KV * D, hid)), WeightSpec("k", (KV * D, hid)), WeightSpec("v", (H * V, hid)),
+                WeightSpec("q.conv", (KV * D, taps), kind="vector"), WeightSpec("k.conv", (KV * D, taps), kind="vector"),
+                WeightSpec("v.conv", (H * V, taps), kind="vector"),
+                WeightSpec("b", (H, hid)), WeightSpec("A_log", (H,), kind="vector", init="zeros"),
+                WeightSpec("norm", (V,), kind="vector", init="norm"),
+                WeightSpec("a1", (self.a_rank, hid)), WeightSpec("a2", (H * D, self.a_rank)),
+                WeightSpec("dt_bias", (H * D,), kind="vector", init="zeros"),
+                WeightSpec("g1", (self.g_rank, hid)), WeightSpec("g2", (H * V, self.g_rank)), WeightSpec("o", (hid, H * V))]
+
+    def cache_need(self):
+        return StateNeed((self.H * self.D * self.V + (self.taps - 1) * self.C,), "float32")
+
+    def load(self, tensors, dtype, device):
+        a1, g1 = tensors.pop("a1"), tensors.pop("g1")
+        self.a2, self.g2 = tensors.pop("a2"), tensors.pop("g2")
+        self.a_rank, self.g_rank = a1.shape[0], g1.shape[0]
+        if self.a2.shape[1] != self.a_rank or self.g2.shape[1] != self.g_rank:
+            raise ValueError("the two halves of a low-rank projection disagree about its rank")
+        # one product for everything that reads the mixer's input: q | k | v | b | a1 | g1
+        self.proj = torch.cat([tensors.pop("q"), tensors.pop("k"), tensors.pop("v"), tensors.pop("b"), a1, g1], dim=0).contiguous()
+        self.conv = torch.cat([tensors.pop("q.conv"), tensors.pop("k.conv"), tensors.pop("v.conv")], dim=0).float().contiguous()
+        self.A_log, self.dt_bias = tensors.pop("A_log").float().contiguous(), tensors.pop("dt_bias").float().contiguous()
+        self.norm = tensors.pop("norm").float().contiguous()
+        self.o = tensors.pop("o")
+
+    @property
+    def open_weight(self):
+        return self.o
+
+    @property
+    def first_weight(self):
+        return self.proj
+
+    def step_flops(self, rows, pairs):
+        return 8 * self.H * self.D * self.V * rows                 # decay, S^T k, rank-one update, read-out
+
+    def forward(self, h, ctx, cache, position, owns_cache=True):
+        rows, w = self.forward_open(h, ctx, cache, position, owns_cache)
+        return ctx.ops.linear(rows, w)
+
+    def forward_open(self, h, ctx, cache, position, owns_cache=True):
+        ops, H, KV, D, V, C = ctx.ops, self.H, self.KV, self.D, self.V, self.C
+        p = ops.linear(h, self.proj)
+        a_in = p[:, C + H:C + H + self.a_rank]
+        g_in = p[:, C + H + self.a_rank:]
+        a = ops.linear(a_in, self.a2)                               # [T, H D]
+        gate = ops.linear(g_in, self.g2)                            # [T, H V]
+        prep = ops.delta_prepare(p, a, self.conv, self.A_log, self.dt_bias, H, KV, D, V, self.taps, self.unit_eps,
+                                 cache.state, ctx.batch)            # float32 q | k | v | beta | g per token; conv tail -> state
+        o = ops.delta_scan(prep, H, KV, D, V, cache.state, ctx.batch)                   # float32 [T, H V]
+        rows = ops.group_rmsnorm_gate(o, self.norm, gate, self.eps, H, V, ctx.dtype)
+        return rows, self.o

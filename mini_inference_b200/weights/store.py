@@ -56,7 +56,7 @@ def check_names(table, files: Dict[str, object], ignorable=()):
     for name, ws in table:
         if name in files:
             dtype, shape = files[name].info(name)
-            if tuple(shape) != tuple(ws.shape):
+            if len(shape) != len(ws.shape) or any(w >= 0 and w != g for g, w in zip(shape, ws.shape)):   # -1: any size
                 wrong_shape.append((name, shape, ws.shape))
             if ws.kind != "table" and not dtype.is_floating_point:
                 wrong_dtype.append((name, dtype))

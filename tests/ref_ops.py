@@ -109,3 +109,167 @@ class TorchRefOps:
     def sample(self, logits, temperatures, seeds, counters):
         from tests.ref_sampling import gumbel_sample_reference
         return gumbel_sample_reference(logits, temperatures, seeds, counters)
+
+
+# ---------------------------------------------------------------- float32 stream, polynomial norm, recurrences, latent attention
+def _rms(x, eps):
+    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+
+
+def _embed_scaled_norm(self, ids, table, g, eps, out_dtype):
+    return (_rms(table[ids.long()].float(), eps) * g.float()).to(out_dtype)
+
+
+def _add_scaled_rmsnorm(self, x, delta, g, eps, rows, pre_add, out_dtype):
+    assert x.dtype == torch.float32
+    if rows is None:
+        if delta is not None:
+            x.add_(delta.float())
+        if pre_add is not None:
+            x.add_(pre_add.float())
+        src = x
+    else:
+        src = x[rows.long()]
+        if delta is not None:
+            src = src + delta[rows.long()].float()
+        if pre_add is not None:
+            src = src + pre_add.float()
+    return (_rms(src, eps) * g.float()).to(out_dtype)
+
+
+def _polynorm(self, z, coef, eps):
+    z32 = z.float()
+    a, b, c, e = coef.float().tolist()
+    return (a * _rms(z32, eps) + b * _rms(z32 ** 2, eps) + c * _rms(z32 ** 3, eps) + e).to(z.dtype)
+
+
+def _segments(batch):
+    qs = batch.host["seg_q_start"]
+    return [(int(qs[i]), int(qs[i + 1]), int(batch.host["seg_slot"][i])) for i in range(batch.num_segs)]
+
+
+def _lightning_scan(self, p, H, D, V, decay, state, batch):
+    T = p.shape[0]
+    silu = torch.nn.functional.silu
+    q = silu(p[:, :H * D].float()).view(T, H, D)
+    k = silu(p[:, H * D:2 * H * D].float()).view(T, H, D)
+    v = silu(p[:, 2 * H * D:2 * H * D + H * V].float()).view(T, H, V)
+    o = torch.zeros(T, H * V, dtype=torch.float32, device=p.device)
+    for a, b, slot in _segments(batch):
+        S = state[slot].view(H, D, V).clone()
+        for t in range(a, b):
+            S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
+            o[t] = torch.einsum("hdv,hd->hv", S, q[t]).reshape(-1)
+        state[slot] = S.reshape(-1)
+    return o
+
+
+def _group_rmsnorm_gate(self, o, weight, gate, eps, groups, gs, out_dtype):
+    T = o.shape[0]
+    y = _rms(o.view(T, groups, gs), eps).reshape(T, groups * gs)
+    y = y * weight.float().repeat(groups * gs // weight.numel())
+    return (y * torch.sigmoid(gate.float())).to(out_dtype)
+
+
+def _delta_prepare(self, p, a, conv, A_log, dt_bias, H, KV, D, V, taps, unit_eps, state, batch):
+    T = p.shape[0]
+    C = 2 * KV * D + H * V
+    x = p[:, :C].float()
+    out = torch.zeros(T, C + H + H * D, dtype=torch.float32, device=p.device)
+    base = H * D * V
+    for s0, s1, slot in _segments(batch):
+        hist = state[slot, base:base + (taps - 1) * C].view(taps - 1, C)
+        ext = torch.cat([hist, x[s0:s1]], dim=0)                           # row i: position first - (taps - 1) + i
+        y = torch.zeros(s1 - s0, C, device=p.device)
+        for j in range(taps):
+            y += conv[:, j].float() * ext[j:j + s1 - s0]
+        y = torch.nn.functional.silu(y)
+        qk = y[:, :2 * KV * D].view(s1 - s0, 2 * KV, D)
+        qk = qk / torch.sqrt(qk.pow(2).sum(-1, keepdim=True) + unit_eps)
+        qk[:, :KV] *= D ** -0.5
+        out[s0:s1, :2 * KV * D] = qk.reshape(s1 - s0, -1)
+        out[s0:s1, 2 * KV * D:C] = y[:, 2 * KV * D:]
+        if taps > 1:
+            state[slot, base:base + (taps - 1) * C] = ext[ext.shape[0] - (taps - 1):].reshape(-1)
+    out[:, C:C + H] = torch.sigmoid(p[:, C:C + H].float())
+    sp = torch.nn.functional.softplus(a.float() + dt_bias.float()).view(T, H, D)
+    out[:, C + H:] = torch.exp(-torch.exp(A_log.float())[None, :, None] * sp).reshape(T, H * D)
+    return out
+
+
+def _delta_scan(self, prep, H, KV, D, V, state, batch):
+    T = prep.shape[0]
+    C = 2 * KV * D + H * V
+    q = prep[:, :KV * D].view(T, KV, D).repeat_interleave(H // KV, dim=1)
+    k = prep[:, KV * D:2 * KV * D].view(T, KV, D).repeat_interleave(H // KV, dim=1)
+    v = prep[:, 2 * KV * D:C].view(T, H, V)
+    beta, g = prep[:, C:C + H], prep[:, C + H:].view(T, H, D)
+    o = torch.zeros(T, H * V, dtype=torch.float32, device=prep.device)
+    for s0, s1, slot in _segments(batch):
+        S = state[slot, :H * D * V].view(H, D, V).clone()
+        for t in range(s0, s1):
+            S = g[t][:, :, None] * S
+            u = beta[t][:, None] * (v[t] - torch.einsum("hdv,hd->hv", S, k[t]))
+            S = S + k[t][:, :, None] * u[:, None, :]
+            o[t] = torch.einsum("hdv,hd->hv", S, q[t]).reshape(-1)
+        state[slot, :H * D * V] = S.reshape(-1)
+    return o
+
+
+def _batched_linear(self, x, col0, head_stride, K, w):
+    H = w.shape[0]
+    if col0 is not None:
+        x = torch.stack([x[:, col0 + h * head_stride:col0 + h * head_stride + K] for h in range(H)])
+    return torch.einsum("htk,hnk->htn", x.float(), w.float()).to(x.dtype)
+
+
+def _rotate_pairs(v, positions, inv_freq):
+    n = inv_freq.numel()
+    ang = positions.float()[:, None] * inv_freq.float()[None, :]
+    shape = (v.shape[0],) + (1,) * (v.dim() - 2) + (n,)
+    c, s = ang.cos().view(shape), ang.sin().view(shape)
+    out = v.clone()
+    a, b = v[..., 0:2 * n:2], v[..., 1:2 * n:2]
+    out[..., 0:2 * n:2] = a * c - b * s
+    out[..., 1:2 * n:2] = b * c + a * s
+    return out
+
+
+def _latent_prepare(self, p, q_abs, H, D, R, C, norm_w, eps, inv_freq, meta, cache):
+    T, dt = p.shape[0], p.dtype
+    qr = p[:, :H * (D + R)].view(T, H, D + R)[:, :, D:].float()
+    q = torch.cat([q_abs.transpose(0, 1).float(), _rotate_pairs(qr, meta.positions, inv_freq)], dim=-1).to(dt)
+    if cache is not None:
+        dkv = p[:, H * (D + R):H * (D + R) + C + R].float()
+        row = torch.cat([_rms(dkv[:, :C], eps) * norm_w.float(), _rotate_pairs(dkv[:, C:], meta.positions, inv_freq)], dim=-1)
+        page, off = meta.slots.long() // meta.page_size, meta.slots.long() % meta.page_size
+        cache[page, 0, off, :] = row.to(cache.dtype)
+    return q.contiguous()
+
+
+def _latent_attention(self, q, cache, meta, H, C, R, scale):
+    T = q.shape[0]
+    out = torch.zeros(H, T, C, dtype=q.dtype, device=q.device)
+    q_start, pos0, kv_len = meta.seg_q_start.tolist(), meta.seg_pos0.tolist(), meta.seg_kv_len.tolist()
+    rows = meta.table_rows.tolist()
+    ps = meta.page_size
+    for s in range(len(pos0)):
+        a, b, L = q_start[s], q_start[s + 1], kv_len[s]
+        j = torch.arange(L, device=q.device)
+        kv = cache[meta.block_table[rows[s], j // ps].long(), 0, j % ps, :].float()         # [L, C + R]
+        pq = pos0[s] + torch.arange(b - a, device=q.device)
+        sc = torch.einsum("phd,jd->hpj", q[a:b].float(), kv) * scale
+        sc = sc.masked_fill(~(j[None, :] <= pq[:, None])[None], float("-inf"))
+        out[:, a:b] = torch.einsum("hpj,jc->hpc", torch.softmax(sc, dim=-1), kv[:, :C]).to(q.dtype)
+    return out
+
+
+def _head_gate(self, o, gate, out_dtype):
+    H, T, V = o.shape
+    return (o.float() * torch.sigmoid(gate.float()).T[:, :, None]).transpose(0, 1).reshape(T, H * V).to(out_dtype)
+
+
+for _name, _fn in list(globals().items()):
+    if _name.startswith("_") and _name[1:] in ("embed_scaled_norm", "add_scaled_rmsnorm", "polynorm", "lightning_scan", "group_rmsnorm_gate",
+                                               "delta_prepare", "delta_scan", "batched_linear", "latent_prepare", "latent_attention", "head_gate"):
+        setattr(TorchRefOps, _name[1:], _fn)
