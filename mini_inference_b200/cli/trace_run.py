@@ -29,7 +29,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (a divisor of 64)")
-    ap.add_argument("--max-live", type=int, default=8, help="state slots: most requests live at a time")
+    ap.add_argument("--max-live", type=int, default=4, help="state slots: most requests live at a time")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
     if args.page_size <= 0 or 64 % args.page_size:

@@ -591,6 +591,154 @@ class CudaOps:
             self.launches += 2 if S > 1 else 1
         return out
 
+    # ---------------------------------------------------------------- float32 stream, scalar norms, polynomial norm
+    def embed_scaled_norm(self, ids, table, g, eps, out_dtype):
+        """x = g * e / rms(e), e = table[ids]: the start of a residual stream (float32 [T, hidden] when out_dtype says so)."""
+        T, hidden = ids.shape[0], table.shape[1]
+        x = torch.empty((T, hidden), dtype=out_dtype, device=table.device)
+        _check(self.lib.mi_embed_scaled_norm(_p(ids), _p(table), _p(g), _p(x), T, hidden, table.shape[0], _c.c_float(eps),
+                                             _code(table.dtype), _code(out_dtype), self._stream()), "embed_scaled_norm")
+        self.launches += 1
+        return x
+
+    def add_scaled_rmsnorm(self, x, delta, g, eps, rows, pre_add, out_dtype):
+        """x (float32 stream) += delta (+ pre_add, a float32 [hidden] vector); y = g * x / rms(x) in out_dtype.
+        rows: normalise only these rows and leave the stream untouched."""
+        assert x.dtype == torch.float32 and x.is_contiguous() and (delta is None or delta.is_contiguous())
+        hidden = x.shape[-1]
+        n = x.shape[0] if rows is None else rows.shape[0]
+        y = torch.empty((n, hidden), dtype=out_dtype, device=x.device)
+        _check(self.lib.mi_add_scaled_rmsnorm(_p(x), _p(delta), _p(pre_add), _p(g), _p(y), _p(rows), n, hidden, _c.c_float(eps),
+                                              _code(delta.dtype if delta is not None else out_dtype), _code(out_dtype),
+                                              self._stream()), "add_scaled_rmsnorm")
+        self.launches += 1
+        return y
+
+    def polynorm(self, z, coef, eps):
+        """a N(z) + b N(z^2) + c N(z^3) + e per row, N(y) = y / rms(y); coef = float32 (a, b, c, e) on the device."""
+        assert z.is_contiguous()
+        out = torch.empty_like(z)
+        _check(self.lib.mi_polynorm(_p(z), _p(coef), _p(out), z.shape[0], z.shape[1], _c.c_float(eps), _code(z.dtype), self._stream()),
+               "polynorm")
+        self.launches += 1
+        return out
+
+    def group_rmsnorm_gate(self, o, weight, gate, eps, groups, gs, out_dtype):
+        """o float32 [T, groups * gs] -> o / rms(o over each group) * weight * sigmoid(gate) in out_dtype.  weight has
+        groups * gs entries (one vector for the row) or gs (shared by the groups); gate [T, groups * gs] may be a strided view."""
+        T = o.shape[0]
+        assert o.dtype == torch.float32 and o.is_contiguous() and gate.stride(1) == 1 and gate.dtype == out_dtype
+        y = torch.empty((T, groups * gs), dtype=out_dtype, device=o.device)
+        _check(self.lib.mi_group_rmsnorm_gate(_p(o), _p(weight), weight.numel(), _p(gate), gate.stride(0), _p(y), T, groups, gs,
+                                              _c.c_float(eps), _code(out_dtype), self._stream()), "group_rmsnorm_gate")
+        self.launches += 1
+        return y
+
+    def head_gate(self, o, gate, out_dtype):
+        """o [H, T, V], gate [T, H] (a strided view is allowed) -> rows [T, H V] = o * sigmoid(gate) per head."""
+        H, T, V = o.shape
+        assert o.is_contiguous() and gate.stride(1) == 1 and o.dtype == out_dtype == gate.dtype
+        y = torch.empty((T, H * V), dtype=out_dtype, device=o.device)
+        _check(self.lib.mi_head_gate(_p(o), _p(gate), gate.stride(0), _p(y), T, H, V, _code(out_dtype), self._stream()), "head_gate")
+        self.launches += 1
+        return y
+
+    # ---------------------------------------------------------------- matrix-state recurrences
+    def lightning_scan(self, p, H, D, V, decay, state, batch):
+        """p [T, >= 2 H D + H V] = q | k | v before silu; state float32 [slots, H D V] (an entry continues from its slot's
+        state and leaves the new one there).  Returns float32 [T, H V]."""
+        T = p.shape[0]
+        assert p.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
+        out = torch.empty((T, H * V), dtype=torch.float32, device=p.device)
+        _check(self.lib.mi_lightning_scan(_p(p), p.stride(0), _p(decay), _p(state), _c.c_longlong(state.stride(0)), _p(out),
+                                          _p(batch.seg_q_start), _p(batch.seg_slot), batch.num_segs, H, D, V, _code(p.dtype),
+                                          self._stream()), "lightning_scan")
+        self.launches += 1
+        return out
+
+    def delta_prepare(self, p, a, conv, A_log, dt_bias, H, KV, D, V, taps, unit_eps, state, batch):
+        """What enters the gated delta rule, in float32 per token: q | k (after convolution, silu, unit norm; q also
+        * D^-1/2) | v (convolution, silu) | beta = sigmoid | g = exp(-exp(A_log) softplus(a + dt_bias)).  The
+        convolutions read the inputs before an entry's first token from the slot (behind the H D V state entries)
+        and leave their last taps - 1 inputs there."""
+        T = p.shape[0]
+        C = 2 * KV * D + H * V
+        assert p.stride(1) == 1 and a.stride(1) == 1 and a.dtype == p.dtype and state.is_contiguous()
+        out = torch.empty((T, C + H + H * D), dtype=torch.float32, device=p.device)
+        _check(self.lib.mi_delta_prepare(_p(p), p.stride(0), _p(a), a.stride(0), _p(conv), _p(A_log), _p(dt_bias), _p(state),
+                                         _c.c_longlong(state.stride(0)), _c.c_longlong(H * D * V), _p(out), out.stride(0),
+                                         _p(batch.token_seg), _p(batch.seg_q_start), _p(batch.seg_slot), T, batch.num_segs,
+                                         H, KV, D, V, taps, _c.c_float(unit_eps), _code(p.dtype), self._stream()), "delta_prepare")
+        self.launches += 2 if taps > 1 else 1
+        return out
+
+    def delta_scan(self, prep, H, KV, D, V, state, batch):
+        """S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q per head, token by token.  float32 [T, H V]."""
+        T = prep.shape[0]
+        out = torch.empty((T, H * V), dtype=torch.float32, device=prep.device)
+        _check(self.lib.mi_delta_scan(_p(prep), prep.stride(0), _p(state), _c.c_longlong(state.stride(0)), _p(out),
+                                      _p(batch.seg_q_start), _p(batch.seg_slot), batch.num_segs, H, KV, D, V, self._stream()),
+               "delta_scan")
+        self.launches += 1
+        return out
+
+    # ---------------------------------------------------------------- latent attention
+    def batched_linear(self, x, col0, head_stride, K, w):
+        """One product per head: w [H, N, K]; x is [T, ...] with head h's K inputs at columns col0 + h * head_stride
+        (col0 given), or [H, T, K].  Returns [H, T, N].  bfloat16: the library's batched product; float32: this
+        package's float32 product, head by head (no reduced-precision mode)."""
+        H, N, _ = w.shape
+        if col0 is not None:
+            T = x.shape[0]
+            xs = torch.as_strided(x, (H, T, K), (head_stride, x.stride(0), 1), x.storage_offset() + col0)
+        else:
+            T, xs = x.shape[1], x
+        if x.dtype != torch.float32:
+            return torch.bmm(xs, w.transpose(1, 2))
+        out = torch.empty((H, T, N), dtype=torch.float32, device=x.device)
+        for h in range(H):
+            _check(self.lib.mi_gemm_f32_nt(_p(xs[h]), xs.stride(1), _p(w[h]), _p(out[h]), N, T, N, K, self._stream()), "gemm_f32")
+        self.launches += H
+        return out
+
+    def latent_prepare(self, p, q_abs, H, D, R, C, norm_w, eps, inv_freq, meta, cache):
+        """p [T, ..] = q heads [H, D + R] | dkv [C + R] | ..; q_abs [H, T, C].  Returns q [T, H, C + R] = [q_abs | rotated
+        q part]; writes the token's cache row [rmsnorm(dkv[:C]) * norm_w | rotated dkv[C:]] at its slot (cache None: no write)."""
+        T = p.shape[0]
+        assert p.stride(1) == 1 and q_abs.is_contiguous()
+        q = torch.empty((T, H, C + R), dtype=p.dtype, device=p.device)
+        nf = 0 if inv_freq is None else inv_freq.numel()
+        _check(self.lib.mi_latent_prepare(_p(p), p.stride(0), _p(q_abs), _p(q), _p(cache), _p(norm_w), _p(inv_freq), nf,
+                                          _p(meta.positions), _p(meta.slots), T, H, D, R, C, _c.c_float(eps), _code(p.dtype),
+                                          self._stream()), "latent_prepare")
+        self.launches += 1
+        return q
+
+    def latent_attention(self, q, cache, meta, H, C, R, scale):
+        """q [T, H, C + R] over the cached rows [c | kr] (cache [pages, 1, page, C + R]); causal softmax; the weighted
+        sum is over the rows' first C entries.  Returns [H, T, C]."""
+        T = q.shape[0]
+        out = torch.empty((H, T, C), dtype=q.dtype, device=q.device)
+        num_decode, num_tiles = meta.decode_segs.shape[0], meta.prefill_tiles.shape[0]
+        code = _code(q.dtype)
+        if num_tiles:
+            _check(self.lib.mi_latent_prefill(_p(q), _p(cache), _p(out), _p(meta.prefill_tiles), num_tiles, _p(meta.seg_q_start),
+                                              _p(meta.seg_pos0), _p(meta.block_table), _p(meta.table_rows), meta.max_pages, T, H, C, R,
+                                              meta.page_size, meta.tile, _c.c_float(scale), code, self._stream()), "latent_prefill")
+            self.launches += 1
+        if num_decode:
+            S = self.choose_splits(num_decode * math.ceil(H / 4), meta.max_kv_len, 2)
+            o_part = lse = None
+            if S > 1:
+                o_part = torch.empty((num_decode, H, S, C), dtype=torch.float32, device=q.device)
+                lse = torch.empty((num_decode, H, S), dtype=torch.float32, device=q.device)
+            _check(self.lib.mi_latent_decode(_p(q), _p(cache), _p(out), _p(o_part), _p(lse), _p(meta.decode_segs), num_decode,
+                                             _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), _p(meta.table_rows),
+                                             meta.max_pages, T, H, C, R, meta.page_size, S, _c.c_float(scale), code, self._stream()),
+                   "latent_decode")
+            self.launches += 2 if S > 1 else 1
+        return out
+
     # ---------------------------------------------------------------- sampling
     def argmax(self, logits):
         return self.sample(logits, None, None, None)
