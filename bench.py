@@ -276,8 +276,51 @@ def reference_arm(args):
     return 0
 
 
+def design_bench(args):
+    """--design naditar: prompt and decode throughput of the Naditar design at layer sizes of real models (random weights),
+    beside Qwen3 dense of the same width, depth, vocabulary and feed-forward parameters, and every new kernel beside its
+    Qwen3 counterpart with its share of the bound it is up against.  One JSON line; the default workload is untouched."""
+    import torch
+
+    from mini_inference_b200.cli import microbench
+    from mini_inference_b200.engine.llm import LLM
+    from mini_inference_b200.ops import get_ops
+
+    pk, vocab, out = peaks(), 65536, {"design": "naditar", "peaks": pk, "sizes": {}}
+    for size in args.design_sizes.split(","):
+        res = {}
+        for name, cfg in (("naditar", microbench.naditar_config(size, args.design_layers, vocab)),
+                          ("qwen3", microbench.qwen3_config_like(size, args.design_layers, vocab))):
+            for tc in ((False, True) if name == "naditar" else (False,)):
+                llm = LLM(None, random_config=cfg, random_seed=0, dtype="bfloat16", device="cuda:0", kv_block_size=16,
+                          kv_cache_tokens=64 * args.ctx + 4096, kv_watermark=0.0, max_num_seqs=64, max_model_len=args.ctx,
+                          max_batched_tokens=4096, cuda_graphs=False)
+                llm.ops.latent_tc = tc
+                pre_ms = prefill(llm, torch, 2048, vocab, warmup=3, reps=5, pause=0.25)
+                llm.enable_cuda_graphs()
+                r = {"prefill_2048_ms": round(pre_ms, 3), "prefill_tok_s": round(2048 / pre_ms * 1e3, 1),
+                     "weight_gb": round(llm.load_info["weight_bytes"] / 1e9, 3)}
+                for b in (1, 8, 64):
+                    d = decode_device(llm, torch, b, args.ctx, max(16, args.steps // 4), args.warmup, vocab)
+                    r[f"decode_b{b}_tok_s"], r[f"decode_b{b}_ms"], r[f"decode_b{b}_launches_per_step"] = \
+                        round(d["tok_s"], 1), round(d["ms"], 4), d["launches"] // max(16, args.steps // 4)
+                llm.ops.latent_tc = False
+                res[name + ("+latent_tc" if tc else "")] = r
+                del llm
+                torch.cuda.empty_cache()
+        out["sizes"][size] = {"layers": args.design_layers, "ctx": args.ctx, "engines": res}
+    if not args.skip_points:
+        margs = argparse.Namespace(design_size=args.design_sizes.split(",")[0], tokens=2048, ctx=args.ctx, iters=20)
+        out["kernels"] = microbench.bench_design(margs, get_ops("cuda:0"), pk["hbm_gbs"], out=lambda *a, **k: print(*a, file=sys.stderr, **k))
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--design", default=None, choices=["naditar"], help="instead of the default workload: this design beside Qwen3 at equal sizes")
+    ap.add_argument("--design-sizes", default="2k,4k")
+    ap.add_argument("--design-layers", type=int, default=8)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
@@ -294,6 +337,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return reference_arm(args)
+    if args.design:
+        return design_bench(args)
 
     import torch
 

@@ -6,6 +6,7 @@ bench/micro/bench_attention.py (:61-167: paged decode attention over batch x con
     python -m mini_inference_b200.cli.microbench gemm      [--rows 1,8,64] [--size 4b]
     python -m mini_inference_b200.cli.microbench attention [--batch 1,8,64] [--ctx 4096]
     python -m mini_inference_b200.cli.microbench prefill   [--tokens 2048] [--ctx-before 0]
+    python -m mini_inference_b200.cli.microbench design    [--design-size 2k|4k]   (the Naditar kernels beside Qwen3's)
 
 Each line: kernel, shape, microseconds (CUDA events, after warm-up), GB/s of the bytes the
 kernel has to read, and that as a share of the measured copy bandwidth."""
@@ -160,9 +161,163 @@ def bench_prefill_attention(args, ops, peak):
     ops.check_errors()
 
 
+# ---------------------------------------------------------------- the kernels of the Naditar design beside their Qwen3 counterparts
+NADITAR_SIZES = {
+    # width, feed-forward, heads and head sizes in the range of 1-3 B and 7-8 B parameter models; the latent rows have 128 entries
+    "2k": dict(width=2048, ff=8192, heads=16, kv_heads=8, dim=128, vdim=128, conv=4, rank=64, l_heads=16, l_dim=64, l_rot=32, l_rank=96, l_vdim=64),
+    "4k": dict(width=4096, ff=12288, heads=32, kv_heads=16, dim=128, vdim=128, conv=4, rank=128, l_heads=16, l_dim=128, l_rot=32, l_rank=96, l_vdim=128),
+}
+
+
+def naditar_config(size, layers, vocab=65536):
+    z = NADITAR_SIZES[size]
+    ff = {"kind": "dense", "ff": z["ff"]}
+    delta = {"type": "channel_delta", "mlp": ff, "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"],
+                                                           "conv": z["conv"], "decay_rank": z["rank"], "gate_rank": z["rank"]}}
+    light = {"type": "lightning", "mlp": ff, "mixer": {"heads": z["heads"], "dim": z["dim"], "vdim": z["vdim"],
+                                                       "decay": [1.0 - 2.0 ** -(2 + 6 * h / z["heads"]) for h in range(z["heads"])]}}
+    lat = {"type": "latent_attention", "mlp": ff,
+           "mixer": {"heads": z["l_heads"], "dim": z["l_dim"], "rot_dim": z["l_rot"], "vdim": z["l_vdim"], "kv_rank": z["l_rank"],
+                     "scale": (z["l_dim"] + z["l_rot"]) ** -0.5, "rot": {"base": 1e6, "dims": z["l_rot"]}}}
+    pattern = [delta, delta, lat, light]
+    return {"architecture": "Naditar", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-6},
+            "layers": [pattern[i % 4] for i in range(layers)]}
+
+
+def qwen3_config_like(size, layers, vocab=65536):
+    """Qwen3 dense of the same width, depth and vocabulary; its three feed-forward matrices hold what Naditar's two do."""
+    z = NADITAR_SIZES[size]
+    return {"architectures": ["Qwen3ForCausalLM"], "hidden_size": z["width"], "num_hidden_layers": layers, "num_attention_heads": z["heads"],
+            "num_key_value_heads": z["kv_heads"], "head_dim": 128, "intermediate_size": z["ff"] * 2 // 3 // 128 * 128, "vocab_size": vocab,
+            "rope_theta": 1e6, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 40960}
+
+
+def bench_design(args, ops, peak, out=print):
+    """Each new kernel at the layer sizes of --design-size, with the bytes or operations it cannot avoid and that as a share
+    of the bound it is up against: the measured copy bandwidth, the measured bf16 tensor peak, or (float32 recurrences and
+    float32 attention weights, which the design prescribes) the float32 FMA rate of the CUDA cores, SMs x 128 x 2 x clock."""
+    import numpy as np
+    z = NADITAR_SIZES[args.design_size]
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    bf16_peak = 1590.0
+    if os.path.isfile(os.path.join(here, "MEASURED_PEAKS.json")):
+        with open(os.path.join(here, "MEASURED_PEAKS.json")) as f:
+            bf16_peak = json.load(f)["bf16_tflops"]
+    props = torch.cuda.get_device_properties(0)
+    fma_peak = props.multi_processor_count * 128 * 2 * 1.965e9 / 1e12             # TFLOP/s at the maximum SM clock
+    rows = []
+
+    def line(kernel, shape, us, amount, bound):
+        if bound == "hbm":
+            got, top, unit = amount / us / 1e3, peak, "GB/s"
+        elif bound == "bf16":
+            got, top, unit = amount / us / 1e6, bf16_peak, "TFLOP/s"
+        else:
+            got, top, unit = amount / us / 1e6, fma_peak, "TFLOP/s (fp32 FMA)"
+        rows.append({"kernel": kernel, "shape": shape, "us": round(us, 2), "achieved": round(got, 1), "unit": unit, "frac": round(got / top, 3)})
+        out(f"{kernel:34s} {shape:38s} {us:9.2f} us {got:9.1f} {unit:20s} {100 * got / top:5.1f} % of bound", flush=True)
+
+    t = lambda a: torch.tensor(np.asarray(a, dtype=np.int32), device="cuda")       # noqa: E731
+    bf = torch.bfloat16
+    W, FF, H, KV, D, V, taps = z["width"], z["ff"], z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["conv"]
+    T, it = args.tokens, args.iters
+    # ---- stream kernels (prompt step of T tokens)
+    x = torch.randn(4, T, W, device="cuda")
+    dl = torch.randn(4, T, W, device="cuda", dtype=bf)
+    g1 = torch.ones(1, device="cuda")
+    us = timed(lambda i: ops.add_scaled_rmsnorm(x[i % 4], dl[i % 4], g1, 1e-6, None, None, bf), it)
+    line("add + scalar rmsnorm (f32 stream)", f"T={T} width={W}", us, T * W * 12.0, "hbm")
+    xb, wn = torch.randn(4, T, W, device="cuda", dtype=bf), torch.ones(W, device="cuda", dtype=bf)
+    us = timed(lambda i: ops.add_rmsnorm(xb[i % 4], dl[i % 4], wn, 1e-6), it)
+    line("  Qwen3: add + rmsnorm (bf16 stream)", f"T={T} width={W}", us, T * W * 8.0, "hbm")
+    zz, coef = torch.randn(4, T, FF, device="cuda", dtype=bf), torch.tensor([0.5, 0.3, 0.2, 0.1], device="cuda")
+    us = timed(lambda i: ops.polynorm(zz[i % 4], coef, 1e-6), it)
+    line("polynorm activation", f"T={T} ff={FF}", us, T * FF * 4.0, "hbm")
+    inter = FF * 2 // 3 // 128 * 128
+    gu = torch.randn(4, T, 2 * inter, device="cuda", dtype=bf)
+    us = timed(lambda i: ops.swiglu(gu[i % 4]), it)
+    line("  Qwen3: swiglu", f"T={T} inter={inter}", us, T * inter * 6.0, "hbm")
+    # ---- recurrences: one prompt of T tokens; decode steps of B requests
+    for B, n in ((1, T), (8, 1), (64, 1)):
+        rows_n = B * n
+        batch = types.SimpleNamespace(seg_q_start=t(np.arange(B + 1) * n), seg_slot=t(np.arange(B) + 1), num_segs=B,
+                                      token_seg=t(np.repeat(np.arange(B), n)))
+        kind = "prompt" if n > 1 else "decode"
+        shape = f"{kind} B={B} T={n} heads={H} {D}x{V}"
+        reps = 4 if n > 1 else max(2, (256 << 20) // (B * H * D * V * 4) + 1)      # decode: rotate through more states than the L2 holds
+        p = torch.randn(rows_n, 2 * H * D + 2 * H * V, device="cuda", dtype=bf)
+        decay = torch.full((H,), 0.99, device="cuda")
+        st = torch.zeros(reps, B + 1, H * D * V, device="cuda")
+        us = timed(lambda i: ops.lightning_scan(p, H, D, V, decay, st[i % reps], batch), it)
+        if n > 1:
+            line("lightning scan", shape, us, 4.0 * H * D * V * rows_n, "fma")
+        else:
+            line("lightning scan", shape, us, 8.0 * B * H * D * V, "hbm")
+        C = 2 * KV * D + H * V
+        pd, a = torch.randn(rows_n, C + H + 2 * z["rank"], device="cuda", dtype=bf), torch.randn(rows_n, H * D, device="cuda", dtype=bf)
+        conv, A_log, dtb = torch.randn(C, taps, device="cuda") * 0.3, torch.zeros(H, device="cuda"), torch.zeros(H * D, device="cuda")
+        st2 = torch.zeros(reps, B + 1, H * D * V + (taps - 1) * C, device="cuda")
+        prep = ops.delta_prepare(pd, a, conv, A_log, dtb, H, KV, D, V, taps, 1e-6, st2[0], batch)
+        us = timed(lambda i: ops.delta_prepare(pd, a, conv, A_log, dtb, H, KV, D, V, taps, 1e-6, st2[i % reps], batch), it)
+        line("delta rule: conv, norms, decay", shape, us, rows_n * (2.0 * (C + H + H * D) + 4.0 * (C + H + H * D)), "hbm")
+        us = timed(lambda i: ops.delta_scan(prep, H, KV, D, V, st2[i % reps], batch), it)
+        if n > 1:
+            line("delta rule scan", shape, us, 8.0 * H * D * V * rows_n, "fma")
+        else:
+            line("delta rule scan", shape, us, 8.0 * B * H * D * V, "hbm")
+        del st, st2
+    # ---- latent attention beside grouped-query attention
+    LH, C, R, ps = z["l_heads"], z["l_rank"], z["l_rot"], 16
+    pages = -(-T // ps)
+    table = (torch.randperm(pages, device="cuda").to(torch.int32) + 1).view(1, pages).contiguous()
+    tiles = dict(prefill_tiles=t([(0, r) for r in range(0, T, 64)]).view(-1, 2), prefill_tiles2=t([(0, r) for r in range(0, T, 128)]).view(-1, 2))
+    meta = types.SimpleNamespace(page_size=ps, tile=64, block_table=table, table_rows=t([0]), max_pages=pages, seg_q_start=t([0, T]), seg_pos0=t([0]),
+                                 seg_kv_len=t([T]), decode_segs=t([]), max_kv_len=T, num_tokens=T, **tiles)
+    cache = torch.randn(4, pages + 1, 1, ps, C + R, device="cuda", dtype=bf)
+    q = torch.randn(T, LH, C + R, device="cuda", dtype=bf)
+    pairs = T * (T + 1) / 2
+    for label, tc, bound in (("float32 weights", False, "fma"), ("tensor cores", True, "bf16")):
+        ops.latent_tc = tc
+        us = timed(lambda i: ops.latent_attention(q, cache[i % 4], meta, LH, C, R, 0.1), max(3, it // (1 if tc else 10)))
+        line(f"latent attention, {label}", f"prompt T={T} heads={LH} rows {C}+{R}", us, 2.0 * LH * (2 * C + R) * pairs, bound)
+    kv = torch.randn(4, 2, pages + 1, KV, ps, 128, device="cuda", dtype=bf)
+    qq = torch.randn(T, H * 128, device="cuda", dtype=bf)
+    meta.table_rows = None
+    us = timed(lambda i: ops.paged_attention(qq, kv[i % 4, 0], kv[i % 4, 1], meta, H, KV, 128, 0.1, None), it)
+    line("  Qwen3: attention", f"prompt T={T} heads={H}/{KV} D=128", us, 4.0 * H * 128 * pairs, "bf16")
+    ctx = args.ctx
+    pages = -(-ctx // ps)
+    for B in (8, 64):
+        layers = max(2, (512 << 20) // (B * pages * ps * (C + R) * 2) + 1)
+        table = (torch.stack([torch.randperm(pages, device="cuda") for _ in range(B)]) + 1 + (torch.arange(B, device="cuda") * pages)[:, None]).to(torch.int32)
+        ar = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+        meta = types.SimpleNamespace(page_size=ps, tile=64, block_table=table.contiguous(), table_rows=ar[:B].contiguous(), max_pages=pages, seg_q_start=ar,
+                                     seg_pos0=torch.full((B,), ctx - 1, dtype=torch.int32, device="cuda"),
+                                     seg_kv_len=torch.full((B,), ctx, dtype=torch.int32, device="cuda"), decode_segs=ar[:B].contiguous(),
+                                     prefill_tiles=torch.zeros((0, 2), dtype=torch.int32, device="cuda"), prefill_tiles2=None, max_kv_len=ctx, num_tokens=B)
+        cache = torch.randn(layers, B * pages + 1, 1, ps, C + R, device="cuda", dtype=bf)
+        q = torch.randn(B, LH, C + R, device="cuda", dtype=bf)
+        for label, tc in (("float32 weights", False), ("tensor cores", True)):
+            ops.latent_tc = tc
+            us = timed(lambda i: ops.latent_attention(q, cache[i % layers], meta, LH, C, R, 0.1), it)
+            line(f"latent attention, {label}", f"decode B={B} ctx={ctx} heads={LH} rows {C}+{R}", us, B * ctx * (C + R) * 2.0, "hbm")
+        del cache
+        layers = max(2, (512 << 20) // (B * pages * ps * KV * 128 * 4) + 1)
+        kv = torch.randn(layers, 2, B * pages + 1, KV, ps, 128, device="cuda", dtype=bf)
+        qq = torch.randn(B, H * 128, device="cuda", dtype=bf)
+        meta.table_rows = None
+        us = timed(lambda i: ops.paged_attention(qq, kv[i % layers, 0], kv[i % layers, 1], meta, H, KV, 128, 0.1, None), it)
+        line("  Qwen3: attention", f"decode B={B} ctx={ctx} heads={H}/{KV} D=128", us, B * ctx * KV * 128 * 4.0, "hbm")
+        del kv
+    ops.latent_tc = False
+    ops.check_errors()
+    return rows
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("what", choices=["gemm", "attention", "prefill"])
+    ap.add_argument("what", choices=["gemm", "attention", "prefill", "design"])
+    ap.add_argument("--design-size", default="2k", choices=sorted(NADITAR_SIZES), help="design: layer sizes of the Naditar kernels")
     ap.add_argument("--size", default="4b", choices=sorted(SIZES))
     ap.add_argument("--rows", default="1,8,64", type=lambda s: [int(v) for v in s.split(",")])
     ap.add_argument("--batch", default="1,8,64", type=lambda s: [int(v) for v in s.split(",")])
@@ -180,7 +335,7 @@ def main(argv=None):
     ops = get_ops("cuda:0")
     peak, src = peak_gbs()
     print(f"# peak {peak} GB/s ({src})")
-    {"gemm": bench_gemm, "attention": bench_attention, "prefill": bench_prefill_attention}[args.what](args, ops, peak)
+    {"gemm": bench_gemm, "attention": bench_attention, "prefill": bench_prefill_attention, "design": bench_design}[args.what](args, ops, peak)
     return 0
 
 

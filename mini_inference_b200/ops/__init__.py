@@ -125,6 +125,10 @@ class CudaOps:
         self.skinny_gemm = True              # few-row products on this package's weight-streaming kernel ...
         self.skinny_max_rows, self.skinny_max_cols = 16, 4096    # ... where it is at least as fast as the library's
         self.fast_attention = True           # tests clear this to run the generic attention kernels in bfloat16
+        # Latent attention whose cached rows have 64 or 128 entries can run on the tensor-core paged attention kernels.  Those
+        # round the softmax weights to bfloat16 before the weighted sum; a design that asks for float32 weights gets the
+        # float32 kernels of csrc/attention_latent.cu unless MI_LATENT_TC=1 (or this flag) says otherwise.
+        self.latent_tc = os.environ.get("MI_LATENT_TC", "0") == "1"
         self.launches = 0                    # kernels of this package launched so far
 
     def _stream(self):
@@ -718,6 +722,11 @@ class CudaOps:
         """q [T, H, C + R] over the cached rows [c | kr] (cache [pages, 1, page, C + R]); causal softmax; the weighted
         sum is over the rows' first C entries.  Returns [H, T, C]."""
         T = q.shape[0]
+        if self.latent_tc and q.dtype == torch.bfloat16 and (C + R) in (64, 128) and meta.page_size % 16 == 0:
+            # one shared key head of size C + R whose rows are also the values: the paged attention kernels on the tensor cores
+            # take it as it is (the pool given as keys AND values); the last R columns of each head's output are dropped
+            o = self.paged_attention(q.view(T, H * (C + R)), cache, cache, meta, H, 1, C + R, scale, None)
+            return o.view(T, H, C + R)[:, :, :C].permute(1, 0, 2)
         out = torch.empty((H, T, C), dtype=q.dtype, device=q.device)
         num_decode, num_tiles = meta.decode_segs.shape[0], meta.prefill_tiles.shape[0]
         code = _code(q.dtype)

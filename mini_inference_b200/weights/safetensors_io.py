@@ -99,4 +99,4 @@ def write_safetensors(path: str, tensors, order=None) -> None:
         for name, shape, dtype, make in items:
             t = make().contiguous()
             assert tuple(t.shape) == tuple(shape) and t.dtype == dtype, name
-            f.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")      # reshape: a 0-d tensor has no bytes view
