@@ -2,15 +2,19 @@
 // per key channel, both over a float32 state S [heads, key_dim, value_dim] that lives in a request's state slot.
 //
 // The columns of S never mix: every update is "row factors times S, plus key times a row vector", and the read-out
-// is S^T q.  So a column is given to LANES = 4 lanes of a warp that hold its rows (row r belongs to lane r % 4) in
-// registers for the whole entry; a warp holds 8 neighbouring columns (a 32-byte piece of every row, so that loading
-// and storing the state moves whole sectors), a block 32.  A block walks the tokens of ONE entry (a prompt portion or
-// a single decoded token) of ONE head in order, staging a few tokens' q, k (g) and v at a time in shared memory; the
+// is S^T q.  So a column is given to LANES = 4 lanes of a warp that hold its rows in registers for the whole entry
+// (lane l owns the rows 4 (l + 4 g) + e, g = 0 .. NG-1, e = 0 .. 3: groups of four neighbouring rows, so that a
+// token's q, k and g come out of shared memory as 16-byte loads without bank conflicts); a warp holds 8 neighbouring
+// columns (a 32-byte piece of every row: loading and storing the state moves whole sectors), a block 32.  A block
+// walks the tokens of ONE entry (a prompt portion or a single decoded token) of ONE head in order.  What a token
+// brings (q, k, g, its 32 values, beta: float32, written by a prologue kernel) is staged a few tokens at a time in
+// one of two shared-memory buffers with cp.async, the next chunk travelling while the current one is worked on.  The
 // two dot products of a token are finished with two shuffles each.  Everything is float32.
 //
-// Before the delta rule runs, a kernel per token applies the short causal convolutions (reading the inputs before
-// the entry's first token from the state slot), silu, the unit norms of q and k, the sigmoid of beta and the decay
-// exp(-exp(A_log) softplus(a + dt_bias)); a small kernel then moves the convolutions' last inputs into the slot.
+// Prologue kernels, one small block per (token, unit): lightning: silu of q, k, v.  Delta rule: the short causal
+// convolutions (the inputs before an entry's first token come from the state slot), silu, the unit norms of q and k,
+// sigmoid(beta logits), and the decay exp(-exp(A_log) softplus(a + dt_bias)); a last kernel then moves the
+// convolutions' newest inputs into the slot.
 #include "common.cuh"
 #include <math.h>
 
@@ -25,165 +29,207 @@ constexpr int SCAN_THREADS = 128;
 __device__ __forceinline__ float silu(float x) { return x / (1.f + expf(-x)); }
 __device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + expf(-x)); }
 
-struct ScanIds {
-    int qs, n, slot, h, l, col, colv, wcol;
+__device__ __forceinline__ void cp16(float* dst, const float* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" :: "n"(N) : "memory"); }
+
+// Where the scan finds a token's numbers in its float32 row (ld floats per token).
+struct ScanLayout {
+    int ld, q_off, k_off, v_off, g_off, b_off;      // q/k: + kv_head * D; v: + head * V; g: + head * D; beta: + head
 };
 
-__device__ __forceinline__ ScanIds scan_ids(const int* seg_q_start, const int* seg_slot, int V) {
-    ScanIds s;
-    const int seg = blockIdx.x;
-    s.qs = seg_q_start[seg];
-    s.n = seg_q_start[seg + 1] - s.qs;
-    s.slot = seg_slot[seg];
-    s.h = blockIdx.y;
+// One chunk of nt tokens into a buffer: q, k (g) rows of Dp floats (D copied, the rest stays zero), v [COLS], beta.
+template <bool DELTA>
+__device__ __forceinline__ void stage_chunk(float* buf, int Dp, int TC, const float* __restrict__ prep, const ScanLayout L,
+                                            int tok0, int nt, int h, int kvh, int D, int V, int col0, bool vec) {
+    float* qsm = buf;
+    float* ksm = qsm + TC * Dp;
+    float* gsm = ksm + TC * Dp;                               // DELTA only
+    float* vsm = DELTA ? gsm + TC * Dp : ksm + TC * Dp;       // [TC, COLS]
+    float* bsm = vsm + TC * COLS;                             // [TC] (DELTA only)
+    const int ncol = min(COLS, V - col0);
+    if (vec) {
+        const int dq = D >> 2, vq = ncol >> 2;
+        for (int idx = threadIdx.x; idx < nt * dq; idx += SCAN_THREADS) {
+            const int tt = idx / dq, c = (idx - tt * dq) << 2;
+            const float* row = prep + (size_t)(tok0 + tt) * L.ld;
+            cp16(qsm + tt * Dp + c, row + L.q_off + kvh * D + c);
+            cp16(ksm + tt * Dp + c, row + L.k_off + kvh * D + c);
+            if (DELTA) cp16(gsm + tt * Dp + c, row + L.g_off + h * D + c);
+        }
+        for (int idx = threadIdx.x; idx < nt * vq; idx += SCAN_THREADS) {
+            const int tt = idx / vq, c = (idx - tt * vq) << 2;
+            cp16(vsm + tt * COLS + c, prep + (size_t)(tok0 + tt) * L.ld + L.v_off + h * V + col0 + c);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < nt * D; idx += SCAN_THREADS) {
+            const int tt = idx / D, c = idx - tt * D;
+            const float* row = prep + (size_t)(tok0 + tt) * L.ld;
+            qsm[tt * Dp + c] = row[L.q_off + kvh * D + c];
+            ksm[tt * Dp + c] = row[L.k_off + kvh * D + c];
+            if (DELTA) gsm[tt * Dp + c] = row[L.g_off + h * D + c];
+        }
+        for (int idx = threadIdx.x; idx < nt * ncol; idx += SCAN_THREADS) {
+            const int tt = idx / ncol, c = idx - tt * ncol;
+            vsm[tt * COLS + c] = prep[(size_t)(tok0 + tt) * L.ld + L.v_off + h * V + col0 + c];
+        }
+    }
+    if (DELTA)
+        for (int tt = threadIdx.x; tt < nt; tt += SCAN_THREADS) bsm[tt] = prep[(size_t)(tok0 + tt) * L.ld + L.b_off + h];
+}
+
+// grid (entries, heads, ceil(V / 32)).  DELTA:  S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.
+// otherwise:  S <- decay[h] S + k v^T; o = S^T q.   NG: groups of four rows per lane (key_dim <= 16 NG).
+template <bool DELTA, int NG>
+__global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(
+        const float* __restrict__ prep, const ScanLayout L, const float* __restrict__ decay, float* __restrict__ state,
+        long long state_stride, float* __restrict__ out, const int* __restrict__ seg_q_start, const int* __restrict__ seg_slot,
+        int H, int KV, int D, int V, int TC, int vec) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int Dp = 16 * NG;
+    const int buf_floats = TC * ((DELTA ? 3 : 2) * Dp + COLS + (DELTA ? 1 : 0));
+    const int buf_stride = (buf_floats + 3) & ~3;
+    const int seg = blockIdx.x, h = blockIdx.y, kvh = h / (H / KV);
+    const int qs = seg_q_start[seg], n = seg_q_start[seg + 1] - qs, slot = seg_slot[seg];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    s.l = lane >> 3;
-    s.wcol = warp * 8 + (lane & 7);
-    s.col = blockIdx.z * COLS + s.wcol;
-    s.colv = s.col < V;
-    return s;
-}
-
-// ------------------------------------------------------------------ lightning: S <- decay S + k v^T; o = S^T q
-// p [T, ldp] holds q | k | v (before silu) at columns 0, H D, 2 H D.  grid (entries, heads, ceil(V / 32)).
-template <typename T, int RP>
-__global__ void __launch_bounds__(SCAN_THREADS) lightning_scan_kernel(
-        const T* __restrict__ p, int ldp, const float* __restrict__ decay, float* __restrict__ state, long long state_stride,
-        float* __restrict__ out, const int* __restrict__ seg_q_start, const int* __restrict__ seg_slot, int H, int D, int V, int TC) {
-    extern __shared__ float sm[];
-    float* qsm = sm;                      // [TC, D]
-    float* ksm = qsm + TC * D;            // [TC, D]
-    float* vsm = ksm + TC * D;            // [TC, COLS]
-    const ScanIds id = scan_ids(seg_q_start, seg_slot, V);
-    float* S = state + (long long)id.slot * state_stride + (long long)id.h * D * V;
-    float s[RP];
+    const int l = lane >> 3, wcol = warp * 8 + (lane & 7), col0 = blockIdx.z * COLS, col = col0 + wcol;
+    const bool colv = col < V;
+    for (int i = threadIdx.x; i < 2 * buf_stride; i += SCAN_THREADS) sm[i] = 0.f;       // the pads beyond D (and V) stay zero
+    float* S = state + (long long)slot * state_stride + (long long)h * D * V;
+    float s[4 * NG];
 #pragma unroll
-    for (int i = 0; i < RP; ++i) {
-        const int r = id.l + LANES * i;
-        s[i] = (r < D && id.colv) ? S[(size_t)r * V + id.col] : 0.f;
-    }
-    const float dec = decay[id.h];
-    for (int t0 = 0; t0 < id.n; t0 += TC) {
-        const int nt = min(TC, id.n - t0);
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < nt * D; idx += SCAN_THREADS) {
-            const int tt = idx / D, d = idx - tt * D;
-            const T* row = p + (size_t)(id.qs + t0 + tt) * ldp + (size_t)id.h * D + d;
-            qsm[idx] = silu(to_f32(row[0]));
-            ksm[idx] = silu(to_f32(row[(size_t)H * D]));
+    for (int g = 0; g < NG; ++g)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = 4 * (l + LANES * g) + e;
+            s[4 * g + e] = (r < D && colv) ? S[(size_t)r * V + col] : 0.f;
         }
-        for (int idx = threadIdx.x; idx < nt * COLS; idx += SCAN_THREADS) {
-            const int tt = idx / COLS, c = idx - tt * COLS, cc = blockIdx.z * COLS + c;
-            vsm[idx] = cc < V ? silu(to_f32(p[(size_t)(id.qs + t0 + tt) * ldp + (size_t)2 * H * D + (size_t)id.h * V + cc])) : 0.f;
+    const float dec = DELTA ? 0.f : decay[h];
+    __syncthreads();
+    const int chunks = (n + TC - 1) / TC;
+    stage_chunk<DELTA>(sm, Dp, TC, prep, L, qs, min(TC, n), h, kvh, D, V, col0, vec != 0);
+    cp_commit();
+    for (int c = 0; c < chunks; ++c) {
+        const int t0 = c * TC, nt = min(TC, n - t0);
+        if (c + 1 < chunks) {
+            stage_chunk<DELTA>(sm + ((c + 1) & 1) * buf_stride, Dp, TC, prep, L, qs + t0 + TC, min(TC, n - t0 - TC), h, kvh, D, V, col0, vec != 0);
+            cp_commit();
+            cp_wait<1>();
+        } else {
+            cp_wait<0>();
         }
         __syncthreads();
+        const float* buf = sm + (c & 1) * buf_stride;
+        const float* qsm = buf;
+        const float* ksm = qsm + TC * Dp;
+        const float* gsm = ksm + TC * Dp;
+        const float* vsm = DELTA ? gsm + TC * Dp : ksm + TC * Dp;
+        const float* bsm = vsm + TC * COLS;
+        // four partial sums per dot product keep the chains of dependent additions short; the lightning loop is unrolled
+        // so that the next token's state update is issued while this token's read-out is still being reduced
+#pragma unroll 2
         for (int tt = 0; tt < nt; ++tt) {
-            const float vv = vsm[tt * COLS + id.wcol];
-            const float* kk = ksm + tt * D;
-            const float* qq = qsm + tt * D;
-            float acc = 0.f;
+            const float vv = vsm[tt * COLS + wcol];
+            const float4* kk = reinterpret_cast<const float4*>(ksm + tt * Dp) + l;
+            const float4* qq = reinterpret_cast<const float4*>(qsm + tt * Dp) + l;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            if (DELTA) {
+                const float4* gg = reinterpret_cast<const float4*>(gsm + tt * Dp) + l;
+                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
-            for (int i = 0; i < RP; ++i) {
-                const int r = id.l + LANES * i;
-                if (r < D) {
-                    s[i] = fmaf(dec, s[i], kk[r] * vv);
-                    acc = fmaf(s[i], qq[r], acc);
+                for (int g = 0; g < NG; ++g) {
+                    const float4 gv = gg[LANES * g], kv = kk[LANES * g];
+                    s[4 * g] *= gv.x; s[4 * g + 1] *= gv.y; s[4 * g + 2] *= gv.z; s[4 * g + 3] *= gv.w;
+                    d0 = fmaf(s[4 * g], kv.x, d0); d1 = fmaf(s[4 * g + 1], kv.y, d1);
+                    d2 = fmaf(s[4 * g + 2], kv.z, d2); d3 = fmaf(s[4 * g + 3], kv.w, d3);
+                }
+                float dot = (d0 + d1) + (d2 + d3);
+                dot += __shfl_xor_sync(0xffffffffu, dot, 8);
+                dot += __shfl_xor_sync(0xffffffffu, dot, 16);
+                const float u = bsm[tt] * (vv - dot);
+#pragma unroll
+                for (int g = 0; g < NG; ++g) {
+                    const float4 kv = kk[LANES * g], qv = qq[LANES * g];
+                    s[4 * g] = fmaf(kv.x, u, s[4 * g]); s[4 * g + 1] = fmaf(kv.y, u, s[4 * g + 1]);
+                    s[4 * g + 2] = fmaf(kv.z, u, s[4 * g + 2]); s[4 * g + 3] = fmaf(kv.w, u, s[4 * g + 3]);
+                    a0 = fmaf(s[4 * g], qv.x, a0); a1 = fmaf(s[4 * g + 1], qv.y, a1);
+                    a2 = fmaf(s[4 * g + 2], qv.z, a2); a3 = fmaf(s[4 * g + 3], qv.w, a3);
+                }
+            } else {
+#pragma unroll
+                for (int g = 0; g < NG; ++g) {
+                    const float4 kv = kk[LANES * g], qv = qq[LANES * g];
+                    s[4 * g] = fmaf(dec, s[4 * g], kv.x * vv); s[4 * g + 1] = fmaf(dec, s[4 * g + 1], kv.y * vv);
+                    s[4 * g + 2] = fmaf(dec, s[4 * g + 2], kv.z * vv); s[4 * g + 3] = fmaf(dec, s[4 * g + 3], kv.w * vv);
+                    a0 = fmaf(s[4 * g], qv.x, a0); a1 = fmaf(s[4 * g + 1], qv.y, a1);
+                    a2 = fmaf(s[4 * g + 2], qv.z, a2); a3 = fmaf(s[4 * g + 3], qv.w, a3);
                 }
             }
+            float acc = (a0 + a1) + (a2 + a3);
             acc += __shfl_xor_sync(0xffffffffu, acc, 8);
             acc += __shfl_xor_sync(0xffffffffu, acc, 16);
-            if (id.l == 0 && id.colv) out[(size_t)(id.qs + t0 + tt) * H * V + (size_t)id.h * V + id.col] = acc;
+            if (l == 0 && colv) out[(size_t)(qs + t0 + tt) * H * V + (size_t)h * V + col] = acc;
         }
+        __syncthreads();                                       // the buffer is free for the chunk after the next
     }
 #pragma unroll
-    for (int i = 0; i < RP; ++i) {
-        const int r = id.l + LANES * i;
-        if (r < D && id.colv) S[(size_t)r * V + id.col] = s[i];
-    }
+    for (int g = 0; g < NG; ++g)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = 4 * (l + LANES * g) + e;
+            if (r < D && colv) S[(size_t)r * V + col] = s[4 * g + e];
+        }
 }
 
-// ------------------------------------------------------------------ delta rule with a decay per key channel
-// prep float32 [T, ld]: q [KV D] | k [KV D] | v [H V] | beta [H] | g [H D] (what delta_prepare_kernel wrote).
-//   S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q   (the read-out sees the token's own write)
-template <int RP>
-__global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
-        const float* __restrict__ prep, int ld, float* __restrict__ state, long long state_stride, float* __restrict__ out,
-        const int* __restrict__ seg_q_start, const int* __restrict__ seg_slot, int H, int KV, int D, int V, int TC) {
-    extern __shared__ float sm[];
-    float* qsm = sm;
-    float* ksm = qsm + TC * D;
-    float* gsm = ksm + TC * D;
-    float* vsm = gsm + TC * D;            // [TC, COLS]
-    float* bsm = vsm + TC * COLS;         // [TC]
-    const ScanIds id = scan_ids(seg_q_start, seg_slot, V);
-    const int kvh = id.h / (H / KV);
-    const int C = 2 * KV * D + H * V;
-    float* S = state + (long long)id.slot * state_stride + (long long)id.h * D * V;
-    float s[RP];
-#pragma unroll
-    for (int i = 0; i < RP; ++i) {
-        const int r = id.l + LANES * i;
-        s[i] = (r < D && id.colv) ? S[(size_t)r * V + id.col] : 0.f;
-    }
-    for (int t0 = 0; t0 < id.n; t0 += TC) {
-        const int nt = min(TC, id.n - t0);
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < nt * D; idx += SCAN_THREADS) {
-            const int tt = idx / D, d = idx - tt * D;
-            const float* row = prep + (size_t)(id.qs + t0 + tt) * ld;
-            qsm[idx] = row[kvh * D + d];
-            ksm[idx] = row[KV * D + kvh * D + d];
-            gsm[idx] = row[C + H + id.h * D + d];
-        }
-        for (int idx = threadIdx.x; idx < nt * COLS; idx += SCAN_THREADS) {
-            const int tt = idx / COLS, c = idx - tt * COLS, cc = blockIdx.z * COLS + c;
-            vsm[idx] = cc < V ? prep[(size_t)(id.qs + t0 + tt) * ld + 2 * KV * D + id.h * V + cc] : 0.f;
-        }
-        for (int tt = threadIdx.x; tt < nt; tt += SCAN_THREADS) bsm[tt] = prep[(size_t)(id.qs + t0 + tt) * ld + C + id.h];
-        __syncthreads();
-        for (int tt = 0; tt < nt; ++tt) {
-            const float vv = vsm[tt * COLS + id.wcol], beta = bsm[tt];
-            const float* kk = ksm + tt * D;
-            const float* qq = qsm + tt * D;
-            const float* gg = gsm + tt * D;
-            float dot = 0.f;
-#pragma unroll
-            for (int i = 0; i < RP; ++i) {
-                const int r = id.l + LANES * i;
-                if (r < D) {
-                    s[i] *= gg[r];
-                    dot = fmaf(s[i], kk[r], dot);
-                }
-            }
-            dot += __shfl_xor_sync(0xffffffffu, dot, 8);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 16);
-            const float u = beta * (vv - dot);
-            float acc = 0.f;
-#pragma unroll
-            for (int i = 0; i < RP; ++i) {
-                const int r = id.l + LANES * i;
-                if (r < D) {
-                    s[i] = fmaf(kk[r], u, s[i]);
-                    acc = fmaf(s[i], qq[r], acc);
-                }
-            }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 8);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 16);
-            if (id.l == 0 && id.colv) out[(size_t)(id.qs + t0 + tt) * H * V + (size_t)id.h * V + id.col] = acc;
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < RP; ++i) {
-        const int r = id.l + LANES * i;
-        if (r < D && id.colv) S[(size_t)r * V + id.col] = s[i];
-    }
+template <bool DELTA>
+int launch_scan(const float* prep, ScanLayout L, const float* decay, float* state, long long state_stride, float* out,
+                const int* seg_q_start, const int* seg_slot, int num_segs, int H, int KV, int D, int V, cudaStream_t stream) {
+    if (num_segs == 0) return 0;
+    if (D > 256 || H > 65535) return -2;
+    const int NG = D <= 32 ? 2 : D <= 64 ? 4 : D <= 128 ? 8 : 16;
+    const int per_token = (DELTA ? 3 : 2) * 16 * NG + COLS + 1;
+    const int TC = per_token * 16 * 2 * 4 <= 48 * 1024 ? 16 : per_token * 8 * 2 * 4 <= 48 * 1024 ? 8 : 4;
+    const size_t smem = 2 * (size_t)((TC * per_token + 3) & ~3) * sizeof(float);
+    // 16-byte copies need every piece on a 16-byte boundary: sizes and offsets in multiples of four floats
+    const int vec = ((uintptr_t)prep % 16 == 0 && D % 4 == 0 && V % 4 == 0 && L.ld % 4 == 0 && L.q_off % 4 == 0 && L.k_off % 4 == 0 &&
+                     L.v_off % 4 == 0 && (!DELTA || L.g_off % 4 == 0)) ? 1 : 0;
+    dim3 grid(num_segs, H, (V + COLS - 1) / COLS);
+#define GO(N) state_scan_kernel<DELTA, N><<<grid, SCAN_THREADS, smem, stream>>>(prep, L, decay, state, state_stride, out, seg_q_start, seg_slot, H, KV, D, V, TC, vec)
+    if (NG == 2) GO(2); else if (NG == 4) GO(4); else if (NG == 8) GO(8); else GO(16);
+#undef GO
+    return (int)cudaGetLastError();
 }
 
-// ------------------------------------------------------------------ what enters the delta rule, per token
+// ------------------------------------------------------------------ lightning prologue: out = silu(p[:, :n]) in float32
+template <typename T>
+__global__ void silu_f32_kernel(const T* __restrict__ p, int ldp, float* __restrict__ out, int n) {
+    const T* row = p + (size_t)blockIdx.x * ldp;
+    float* o = out + (size_t)blockIdx.x * n;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) o[i] = silu(to_f32(row[i]));
+}
+
+// ------------------------------------------------------------------ delta-rule prologue, one block per (token, unit)
 // p [T, ldp]: q | k | v (C = 2 KV D + H V channels that pass the convolution) | beta logits [H] | ...
 // a [T, lda]: decay logits [H D].  conv [C, taps], the last tap multiplies the current token.  The inputs of the
 // taps - 1 positions before an entry's first token are rows of hist = state[slot] + hist_off, [taps - 1, C]
 // (zeros for a request's first entry: the slot is zeroed when it is claimed).
+// Units: 0 .. 2 KV - 1 a q or k head (convolution, silu, unit norm; q also * D^-1/2); then H value heads
+// (convolution, silu); then H decay heads; then one unit for all beta.  out [T, ldo]: q | k | v | g | beta (ldo may pad).
+template <typename T>
+__device__ __forceinline__ float conv_silu(const T* __restrict__ p, int ldp, const float* __restrict__ conv, const float* __restrict__ hist,
+                                           int C, int taps, int qs, int r, int c) {
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {
+        const int off = r - (taps - 1 - j);
+        const float x = off >= 0 ? to_f32(p[(size_t)(qs + off) * ldp + c]) : hist[(size_t)(taps - 1 + off) * C + c];
+        acc = fmaf(conv[(size_t)c * taps + j], x, acc);
+    }
+    return silu(acc);
+}
+
 template <typename T>
 __global__ void delta_prepare_kernel(const T* __restrict__ p, int ldp, const T* __restrict__ a, int lda,
                                      const float* __restrict__ conv, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
@@ -191,35 +237,31 @@ __global__ void delta_prepare_kernel(const T* __restrict__ p, int ldp, const T* 
                                      float* __restrict__ out, int ldo, const int* __restrict__ token_seg,
                                      const int* __restrict__ seg_q_start, const int* __restrict__ seg_slot,
                                      int H, int KV, int D, int V, int taps, float unit_eps) {
-    extern __shared__ float y[];          // [C]
-    const int t = blockIdx.x, seg = token_seg[t], qs = seg_q_start[seg], r = t - qs;
+    __shared__ float scratch[32];
+    const int t = blockIdx.x, unit = blockIdx.y, seg = token_seg[t], qs = seg_q_start[seg], r = t - qs;
     const int C = 2 * KV * D + H * V;
     const float* hist = state + (long long)seg_slot[seg] * state_stride + hist_off;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        float acc = 0.f;
-        for (int j = 0; j < taps; ++j) {
-            const int off = r - (taps - 1 - j);
-            const float x = off >= 0 ? to_f32(p[(size_t)(qs + off) * ldp + c]) : hist[(size_t)(taps - 1 + off) * C + c];
-            acc = fmaf(conv[(size_t)c * taps + j], x, acc);
-        }
-        y[c] = silu(acc);
-    }
-    __syncthreads();
     float* o = out + (size_t)t * ldo;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-    for (int hd = warp; hd < 2 * KV; hd += warps) {          // unit vectors; q is also scaled by D^-1/2
+    if (unit < 2 * KV) {
+        const int c0 = unit * D;
         float ss = 0.f;
-        for (int d = lane; d < D; d += 32) ss += y[hd * D + d] * y[hd * D + d];
-        float inv = 1.f / sqrtf(warp_sum(ss) + unit_eps);
-        if (hd < KV) inv *= rsqrtf((float)D);
-        for (int d = lane; d < D; d += 32) o[hd * D + d] = y[hd * D + d] * inv;
-    }
-    for (int c = 2 * KV * D + threadIdx.x; c < C; c += blockDim.x) o[c] = y[c];
-    for (int h = threadIdx.x; h < H; h += blockDim.x) o[C + h] = sigmoidf(to_f32(p[(size_t)t * ldp + C + h]));
-    for (int i = threadIdx.x; i < H * D; i += blockDim.x) {
-        const float x = to_f32(a[(size_t)t * lda + i]) + dt_bias[i];
-        const float sp = x > 20.f ? x : log1pf(expf(x));
-        o[C + H + i] = expf(-expf(A_log[i / D]) * sp);
+        for (int d = threadIdx.x; d < D; d += 128) { const float y = conv_silu(p, ldp, conv, hist, C, taps, qs, r, c0 + d); ss += y * y; }
+        float inv = 1.f / sqrtf(block_sum<128>(ss, scratch) + unit_eps);
+        if (unit < KV) inv *= rsqrtf((float)D);
+        for (int d = threadIdx.x; d < D; d += 128) o[c0 + d] = conv_silu(p, ldp, conv, hist, C, taps, qs, r, c0 + d) * inv;
+    } else if (unit < 2 * KV + H) {
+        const int c0 = 2 * KV * D + (unit - 2 * KV) * V;
+        for (int i = threadIdx.x; i < V; i += 128) o[c0 + i] = conv_silu(p, ldp, conv, hist, C, taps, qs, r, c0 + i);
+    } else if (unit < 2 * KV + 2 * H) {
+        const int hh = unit - 2 * KV - H;
+        const float rate = expf(A_log[hh]);
+        for (int d = threadIdx.x; d < D; d += 128) {
+            const float x = to_f32(a[(size_t)t * lda + hh * D + d]) + dt_bias[hh * D + d];
+            const float sp = x > 20.f ? x : log1pf(expf(x));
+            o[C + hh * D + d] = expf(-rate * sp);
+        }
+    } else {
+        for (int h = threadIdx.x; h < H; h += 128) o[C + H * D + h] = sigmoidf(to_f32(p[(size_t)t * ldp + C + h]));
     }
 }
 
@@ -238,40 +280,28 @@ __global__ void conv_tail_kernel(const T* __restrict__ p, int ldp, float* __rest
     }
 }
 
-inline int pick_chunk(int floats_per_token) {      // tokens staged at a time: 16, or 8 when 16 would pass 48 KB
-    return floats_per_token * 16 * 4 <= 48 * 1024 ? 16 : 8;
-}
-
 }  // namespace
 
-MI_EXPORT int mi_lightning_scan(const void* p, int ldp, const float* decay, float* state, long long state_stride, float* out,
-                                const int* seg_q_start, const int* seg_slot, int num_segs, int H, int D, int V, int dtype,
+// p [T, ldp] = q | k | v before silu (2 H D + H V columns); prep: float32 scratch [T, 2 H D + H V]; out float32 [T, H V].
+MI_EXPORT int mi_lightning_scan(const void* p, int ldp, float* prep, const float* decay, float* state, long long state_stride, float* out,
+                                const int* seg_q_start, const int* seg_slot, int T_, int num_segs, int H, int D, int V, int dtype,
                                 cudaStream_t stream) {
-    if (num_segs == 0) return 0;
-    if (D > 256 || H > 65535) return -2;
-    const int TC = pick_chunk(2 * D + COLS);
-    const size_t smem = (size_t)TC * (2 * D + COLS) * sizeof(float);
-    dim3 grid(num_segs, H, (V + COLS - 1) / COLS);
-#define GO(T, RP) lightning_scan_kernel<T, RP><<<grid, SCAN_THREADS, smem, stream>>>((const T*)p, ldp, decay, state, state_stride, out, \
-                                                                                      seg_q_start, seg_slot, H, D, V, TC)
-#define PICK(T) do { if (D <= 32) GO(T, 8); else if (D <= 64) GO(T, 16); else if (D <= 128) GO(T, 32); else GO(T, 64); } while (0)
-    if (dtype == MI_BF16) PICK(__nv_bfloat16); else PICK(float);
-#undef PICK
-#undef GO
-    return (int)cudaGetLastError();
+    if (num_segs == 0 || T_ == 0) return 0;
+    const int n = 2 * H * D + H * V;
+    dim3 pgrid(T_, T_ >= 256 ? 1 : min(8, (n + 255) / 256));
+    if (dtype == MI_BF16) silu_f32_kernel<__nv_bfloat16><<<pgrid, 256, 0, stream>>>((const __nv_bfloat16*)p, ldp, prep, n);
+    else silu_f32_kernel<float><<<pgrid, 256, 0, stream>>>((const float*)p, ldp, prep, n);
+    int err = (int)cudaGetLastError();
+    if (err) return err;
+    ScanLayout L{n, 0, H * D, 2 * H * D, 0, 0};
+    return launch_scan<false>(prep, L, decay, state, state_stride, out, seg_q_start, seg_slot, num_segs, H, H, D, V, stream);
 }
 
 MI_EXPORT int mi_delta_scan(const float* prep, int ld, float* state, long long state_stride, float* out, const int* seg_q_start,
                             const int* seg_slot, int num_segs, int H, int KV, int D, int V, cudaStream_t stream) {
-    if (num_segs == 0) return 0;
-    if (D > 256 || H > 65535) return -2;
-    const int TC = pick_chunk(3 * D + COLS + 1);
-    const size_t smem = (size_t)TC * (3 * D + COLS + 1) * sizeof(float);
-    dim3 grid(num_segs, H, (V + COLS - 1) / COLS);
-#define GO(RP) delta_scan_kernel<RP><<<grid, SCAN_THREADS, smem, stream>>>(prep, ld, state, state_stride, out, seg_q_start, seg_slot, H, KV, D, V, TC)
-    if (D <= 32) GO(8); else if (D <= 64) GO(16); else if (D <= 128) GO(32); else GO(64);
-#undef GO
-    return (int)cudaGetLastError();
+    const int C = 2 * KV * D + H * V;
+    ScanLayout L{ld, 0, KV * D, 2 * KV * D, C, C + H * D};
+    return launch_scan<true>(prep, L, nullptr, state, state_stride, out, seg_q_start, seg_slot, num_segs, H, KV, D, V, stream);
 }
 
 MI_EXPORT int mi_delta_prepare(const void* p, int ldp, const void* a, int lda, const float* conv, const float* A_log, const float* dt_bias,
@@ -280,19 +310,16 @@ MI_EXPORT int mi_delta_prepare(const void* p, int ldp, const void* a, int lda, c
                                float unit_eps, int dtype, cudaStream_t stream) {
     if (T_ == 0) return 0;
     const int C = 2 * KV * D + H * V;
-    const size_t smem = (size_t)C * sizeof(float);
-    if (smem > 200 * 1024) return -2;
-    if (dtype == MI_BF16) {
-        auto k = delta_prepare_kernel<__nv_bfloat16>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        k<<<T_, 256, smem, stream>>>((const __nv_bfloat16*)p, ldp, (const __nv_bfloat16*)a, lda, conv, A_log, dt_bias, state, state_stride,
-                                     hist_off, out, ldo, token_seg, seg_q_start, seg_slot, H, KV, D, V, taps, unit_eps);
-    } else {
-        auto k = delta_prepare_kernel<float>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        k<<<T_, 256, smem, stream>>>((const float*)p, ldp, (const float*)a, lda, conv, A_log, dt_bias, state, state_stride, hist_off, out, ldo,
-                                     token_seg, seg_q_start, seg_slot, H, KV, D, V, taps, unit_eps);
-    }
+    const int units = 2 * KV + 2 * H + 1;
+    if (units > 65535) return -2;
+    dim3 pgrid(T_, units);
+    if (dtype == MI_BF16)
+        delta_prepare_kernel<__nv_bfloat16><<<pgrid, 128, 0, stream>>>((const __nv_bfloat16*)p, ldp, (const __nv_bfloat16*)a, lda, conv, A_log, dt_bias,
+                                                                       state, state_stride, hist_off, out, ldo, token_seg, seg_q_start, seg_slot,
+                                                                       H, KV, D, V, taps, unit_eps);
+    else
+        delta_prepare_kernel<float><<<pgrid, 128, 0, stream>>>((const float*)p, ldp, (const float*)a, lda, conv, A_log, dt_bias, state, state_stride,
+                                                               hist_off, out, ldo, token_seg, seg_q_start, seg_slot, H, KV, D, V, taps, unit_eps);
     int err = (int)cudaGetLastError();
     if (err || taps <= 1) return err;
     dim3 grid(num_segs, (C + 255) / 256);

@@ -654,21 +654,23 @@ class CudaOps:
         T = p.shape[0]
         assert p.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
         out = torch.empty((T, H * V), dtype=torch.float32, device=p.device)
-        _check(self.lib.mi_lightning_scan(_p(p), p.stride(0), _p(decay), _p(state), _c.c_longlong(state.stride(0)), _p(out),
-                                          _p(batch.seg_q_start), _p(batch.seg_slot), batch.num_segs, H, D, V, _code(p.dtype),
+        prep = torch.empty((T, 2 * H * D + H * V), dtype=torch.float32, device=p.device)      # silu(q | k | v), what the scan stages
+        _check(self.lib.mi_lightning_scan(_p(p), p.stride(0), _p(prep), _p(decay), _p(state), _c.c_longlong(state.stride(0)), _p(out),
+                                          _p(batch.seg_q_start), _p(batch.seg_slot), T, batch.num_segs, H, D, V, _code(p.dtype),
                                           self._stream()), "lightning_scan")
-        self.launches += 1
+        self.launches += 2
         return out
 
     def delta_prepare(self, p, a, conv, A_log, dt_bias, H, KV, D, V, taps, unit_eps, state, batch):
         """What enters the gated delta rule, in float32 per token: q | k (after convolution, silu, unit norm; q also
-        * D^-1/2) | v (convolution, silu) | beta = sigmoid | g = exp(-exp(A_log) softplus(a + dt_bias)).  The
+        * D^-1/2) | v (convolution, silu) | g = exp(-exp(A_log) softplus(a + dt_bias)) | beta = sigmoid (rows padded to a
+        multiple of four floats, so that the scan can fetch them in 16-byte pieces).  The
         convolutions read the inputs before an entry's first token from the slot (behind the H D V state entries)
         and leave their last taps - 1 inputs there."""
         T = p.shape[0]
         C = 2 * KV * D + H * V
         assert p.stride(1) == 1 and a.stride(1) == 1 and a.dtype == p.dtype and state.is_contiguous()
-        out = torch.empty((T, C + H + H * D), dtype=torch.float32, device=p.device)
+        out = torch.empty((T, (C + H * D + H + 3) // 4 * 4), dtype=torch.float32, device=p.device)
         _check(self.lib.mi_delta_prepare(_p(p), p.stride(0), _p(a), a.stride(0), _p(conv), _p(A_log), _p(dt_bias), _p(state),
                                          _c.c_longlong(state.stride(0)), _c.c_longlong(H * D * V), _p(out), out.stride(0),
                                          _p(batch.token_seg), _p(batch.seg_q_start), _p(batch.seg_slot), T, batch.num_segs,

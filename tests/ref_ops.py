@@ -175,7 +175,7 @@ def _delta_prepare(self, p, a, conv, A_log, dt_bias, H, KV, D, V, taps, unit_eps
     T = p.shape[0]
     C = 2 * KV * D + H * V
     x = p[:, :C].float()
-    out = torch.zeros(T, C + H + H * D, dtype=torch.float32, device=p.device)
+    out = torch.zeros(T, (C + H * D + H + 3) // 4 * 4, dtype=torch.float32, device=p.device)      # q | k | v | g | beta | padding
     base = H * D * V
     for s0, s1, slot in _segments(batch):
         hist = state[slot, base:base + (taps - 1) * C].view(taps - 1, C)
@@ -191,9 +191,9 @@ def _delta_prepare(self, p, a, conv, A_log, dt_bias, H, KV, D, V, taps, unit_eps
         out[s0:s1, 2 * KV * D:C] = y[:, 2 * KV * D:]
         if taps > 1:
             state[slot, base:base + (taps - 1) * C] = ext[ext.shape[0] - (taps - 1):].reshape(-1)
-    out[:, C:C + H] = torch.sigmoid(p[:, C:C + H].float())
+    out[:, C + H * D:C + H * D + H] = torch.sigmoid(p[:, C:C + H].float())
     sp = torch.nn.functional.softplus(a.float() + dt_bias.float()).view(T, H, D)
-    out[:, C + H:] = torch.exp(-torch.exp(A_log.float())[None, :, None] * sp).reshape(T, H * D)
+    out[:, C:C + H * D] = torch.exp(-torch.exp(A_log.float())[None, :, None] * sp).reshape(T, H * D)
     return out
 
 
@@ -203,7 +203,7 @@ def _delta_scan(self, prep, H, KV, D, V, state, batch):
     q = prep[:, :KV * D].view(T, KV, D).repeat_interleave(H // KV, dim=1)
     k = prep[:, KV * D:2 * KV * D].view(T, KV, D).repeat_interleave(H // KV, dim=1)
     v = prep[:, 2 * KV * D:C].view(T, H, V)
-    beta, g = prep[:, C:C + H], prep[:, C + H:].view(T, H, D)
+    g, beta = prep[:, C:C + H * D].view(T, H, D), prep[:, C + H * D:C + H * D + H]
     o = torch.zeros(T, H * V, dtype=torch.float32, device=prep.device)
     for s0, s1, slot in _segments(batch):
         S = state[slot, :H * D * V].view(H, D, V).clone()

@@ -502,7 +502,8 @@ def test_kernels_against_the_stand_ins():
         sa, sb = st.clone().to(dev), st.clone()
         pa = ops.delta_prepare(p.to(dev), a.to(dev), conv.to(dev), A_log.to(dev), dtb.to(dev), H, KV, D, V, taps, 1e-6, sa, dbatch)
         pb = ref.delta_prepare(p, a, conv, A_log, dtb, H, KV, D, V, taps, 1e-6, sb, batch)
-        assert close(pa, pb) and close(sa, sb)                   # the convolutions' last inputs moved into the slots
+        n = C + H * D + H                                       # behind these the rows are padding
+        assert close(pa[:, :n], pb[:, :n]) and close(sa, sb)                   # the convolutions' last inputs moved into the slots
         assert close(ops.delta_scan(pa, H, KV, D, V, sa, dbatch), ref.delta_scan(pb, H, KV, D, V, sb, batch), 1e-4)
         assert close(sa, sb, 1e-4)
     ops.check_errors()
