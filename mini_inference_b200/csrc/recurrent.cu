@@ -2,14 +2,19 @@
 // per key channel, both over a float32 state S [heads, key_dim, value_dim] that lives in a request's state slot.
 //
 // The columns of S never mix: every update is "row factors times S, plus key times a row vector", and the read-out
-// is S^T q.  So a column is given to LANES = 4 lanes of a warp that hold its rows in registers for the whole entry
-// (lane l owns the rows 4 (l + 4 g) + e, g = 0 .. NG-1, e = 0 .. 3: groups of four neighbouring rows, so that a
-// token's q, k and g come out of shared memory as 16-byte loads without bank conflicts); a warp holds 8 neighbouring
-// columns (a 32-byte piece of every row: loading and storing the state moves whole sectors), a block 32.  A block
+// is S^T q.  So a PAIR of neighbouring columns is given to LN lanes of a warp that hold its rows in registers for the
+// whole entry (lane l owns the rows 4 (l + LN g) + e, g = 0 .. NG-1, e = 0 .. 3: groups of four neighbouring rows, so
+// that the lanes fetch a token's q, k and g from shared memory as full wavefronts of 16-byte loads, and each fetched
+// number serves two columns).  With LN = 8 a warp holds 4 pairs = 8 neighbouring columns (a 32-byte piece of every
+// row: loading and storing the state moves whole sectors) and a block 32: the form for decode steps.  For prompt
+// portions what counts is the chain of dependent instructions per token, so LN grows to 16 or 32 (one group of four
+// rows per lane) and eight times as many warps share a head.  A block
 // walks the tokens of ONE entry (a prompt portion or a single decoded token) of ONE head in order.  What a token
 // brings (q, k, g, its 32 values, beta: float32, written by a prologue kernel) is staged a few tokens at a time in
 // one of two shared-memory buffers with cp.async, the next chunk travelling while the current one is worked on.  The
-// two dot products of a token are finished with two shuffles each.  Everything is float32.
+// delta rule's S^T k of a token's two columns is finished together with log2(LN) + 1 shuffles, since the update needs it;
+// the partial sums of the read-out S^T q wait in shared memory and are added up (in lane order) and stored, coalesced,
+// once per chunk.  Everything is float32.
 //
 // Prologue kernels, one small block per (token, unit): lightning: silu of q, k, v.  Delta rule: the short causal
 // convolutions (the inputs before an entry's first token come from the state slot), silu, the unit norms of q and k,
@@ -22,9 +27,11 @@ using namespace mi;
 
 namespace {
 
-constexpr int LANES = 4;          // lanes per column
-constexpr int COLS = 32;          // columns per block (4 warps x 8)
 constexpr int SCAN_THREADS = 128;
+// LN lanes share a pair of columns (8: a warp holds 4 pairs, the state moves in 32-byte pieces, few blocks: decode steps,
+// where the state's bytes are the cost; 16 or 32: fewer rows per lane, so a token's chain of dependent instructions is
+// shorter and more warps share the work: prompt portions, where the tokens' latency is the cost).  Columns per block:
+constexpr int cols_of(int LN) { return 4 * (32 / LN) * 2; }
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + expf(-x)); }
 __device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + expf(-x)); }
@@ -42,7 +49,7 @@ struct ScanLayout {
 };
 
 // One chunk of nt tokens into a buffer: q, k (g) rows of Dp floats (D copied, the rest stays zero), v [COLS], beta.
-template <bool DELTA>
+template <bool DELTA, int COLS>
 __device__ __forceinline__ void stage_chunk(float* buf, int Dp, int TC, const float* __restrict__ prep, const ScanLayout L,
                                             int tok0, int nt, int h, int kvh, int D, int V, int col0, bool vec) {
     float* qsm = buf;
@@ -81,41 +88,55 @@ __device__ __forceinline__ void stage_chunk(float* buf, int Dp, int TC, const fl
         for (int tt = threadIdx.x; tt < nt; tt += SCAN_THREADS) bsm[tt] = prep[(size_t)(tok0 + tt) * L.ld + L.b_off + h];
 }
 
-// grid (entries, heads, ceil(V / 32)).  DELTA:  S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.
-// otherwise:  S <- decay[h] S + k v^T; o = S^T q.   NG: groups of four rows per lane (key_dim <= 16 NG).
-template <bool DELTA, int NG>
+// Sums a0 and a1 over the LN row lanes of a column pair (the low lane bits) with log2(LN) + 1 shuffles; every lane gets both.
+template <int LN>
+__device__ __forceinline__ float2 reduce_pair(float a0, float a1, int l) {
+    const bool odd = l & 1;
+    float keep = odd ? a1 : a0;
+    keep += __shfl_xor_sync(0xffffffffu, odd ? a0 : a1, 1);
+#pragma unroll
+    for (int o = 2; o < LN; o <<= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
+    const float other = __shfl_xor_sync(0xffffffffu, keep, 1);
+    return odd ? make_float2(other, keep) : make_float2(keep, other);
+}
+
+// grid (entries, heads, ceil(V / cols_of(LN))).  DELTA:  S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.
+// otherwise:  S <- decay[h] S + k v^T; o = S^T q.   NG: groups of four rows per lane (key_dim <= 4 LN NG).
+template <bool DELTA, int LN, int NG>
 __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(
         const float* __restrict__ prep, const ScanLayout L, const float* __restrict__ decay, float* __restrict__ state,
         long long state_stride, float* __restrict__ out, const int* __restrict__ seg_q_start, const int* __restrict__ seg_slot,
         int H, int KV, int D, int V, int TC, int vec) {
     extern __shared__ __align__(16) float sm[];
-    constexpr int Dp = 16 * NG;
+    constexpr int LANES = LN, COLS = cols_of(LN), Dp = 4 * LN * NG;
     const int buf_floats = TC * ((DELTA ? 3 : 2) * Dp + COLS + (DELTA ? 1 : 0));
     const int buf_stride = (buf_floats + 3) & ~3;
+    float* part = sm + 2 * buf_stride;                         // [TC, COLS, LN + 1] partial sums of the read-out
     const int seg = blockIdx.x, h = blockIdx.y, kvh = h / (H / KV);
     const int qs = seg_q_start[seg], n = seg_q_start[seg + 1] - qs, slot = seg_slot[seg];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int l = lane >> 3, wcol = warp * 8 + (lane & 7), col0 = blockIdx.z * COLS, col = col0 + wcol;
-    const bool colv = col < V;
+    const int l = lane & (LANES - 1), wcol = (warp * (32 / LANES) + lane / LANES) * 2, col0 = blockIdx.z * COLS, col = col0 + wcol;
+    const bool v0 = col < V, v1 = col + 1 < V;
     for (int i = threadIdx.x; i < 2 * buf_stride; i += SCAN_THREADS) sm[i] = 0.f;       // the pads beyond D (and V) stay zero
     float* S = state + (long long)slot * state_stride + (long long)h * D * V;
-    float s[4 * NG];
+    float s0[4 * NG], s1[4 * NG];
 #pragma unroll
     for (int g = 0; g < NG; ++g)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int r = 4 * (l + LANES * g) + e;
-            s[4 * g + e] = (r < D && colv) ? S[(size_t)r * V + col] : 0.f;
+            s0[4 * g + e] = (r < D && v0) ? S[(size_t)r * V + col] : 0.f;
+            s1[4 * g + e] = (r < D && v1) ? S[(size_t)r * V + col + 1] : 0.f;
         }
     const float dec = DELTA ? 0.f : decay[h];
     __syncthreads();
     const int chunks = (n + TC - 1) / TC;
-    stage_chunk<DELTA>(sm, Dp, TC, prep, L, qs, min(TC, n), h, kvh, D, V, col0, vec != 0);
+    stage_chunk<DELTA, COLS>(sm, Dp, TC, prep, L, qs, min(TC, n), h, kvh, D, V, col0, vec != 0);
     cp_commit();
     for (int c = 0; c < chunks; ++c) {
         const int t0 = c * TC, nt = min(TC, n - t0);
         if (c + 1 < chunks) {
-            stage_chunk<DELTA>(sm + ((c + 1) & 1) * buf_stride, Dp, TC, prep, L, qs + t0 + TC, min(TC, n - t0 - TC), h, kvh, D, V, col0, vec != 0);
+            stage_chunk<DELTA, COLS>(sm + ((c + 1) & 1) * buf_stride, Dp, TC, prep, L, qs + t0 + TC, min(TC, n - t0 - TC), h, kvh, D, V, col0, vec != 0);
             cp_commit();
             cp_wait<1>();
         } else {
@@ -128,77 +149,104 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(
         const float* gsm = ksm + TC * Dp;
         const float* vsm = DELTA ? gsm + TC * Dp : ksm + TC * Dp;
         const float* bsm = vsm + TC * COLS;
-        // four partial sums per dot product keep the chains of dependent additions short; the lightning loop is unrolled
-        // so that the next token's state update is issued while this token's read-out is still being reduced
-#pragma unroll 2
+        // two partial sums per dot product and column keep the chains of dependent additions short
         for (int tt = 0; tt < nt; ++tt) {
-            const float vv = vsm[tt * COLS + wcol];
+            const float2 vv = *reinterpret_cast<const float2*>(vsm + tt * COLS + wcol);
             const float4* kk = reinterpret_cast<const float4*>(ksm + tt * Dp) + l;
             const float4* qq = reinterpret_cast<const float4*>(qsm + tt * Dp) + l;
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;                 // a: first column, b: second column
             if (DELTA) {
                 const float4* gg = reinterpret_cast<const float4*>(gsm + tt * Dp) + l;
-                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+                float d0 = 0.f, d1 = 0.f, e0 = 0.f, e1 = 0.f;
 #pragma unroll
                 for (int g = 0; g < NG; ++g) {
                     const float4 gv = gg[LANES * g], kv = kk[LANES * g];
-                    s[4 * g] *= gv.x; s[4 * g + 1] *= gv.y; s[4 * g + 2] *= gv.z; s[4 * g + 3] *= gv.w;
-                    d0 = fmaf(s[4 * g], kv.x, d0); d1 = fmaf(s[4 * g + 1], kv.y, d1);
-                    d2 = fmaf(s[4 * g + 2], kv.z, d2); d3 = fmaf(s[4 * g + 3], kv.w, d3);
+                    s0[4 * g] *= gv.x; s0[4 * g + 1] *= gv.y; s0[4 * g + 2] *= gv.z; s0[4 * g + 3] *= gv.w;
+                    s1[4 * g] *= gv.x; s1[4 * g + 1] *= gv.y; s1[4 * g + 2] *= gv.z; s1[4 * g + 3] *= gv.w;
+                    d0 = fmaf(s0[4 * g], kv.x, d0); d1 = fmaf(s0[4 * g + 1], kv.y, d1);
+                    d0 = fmaf(s0[4 * g + 2], kv.z, d0); d1 = fmaf(s0[4 * g + 3], kv.w, d1);
+                    e0 = fmaf(s1[4 * g], kv.x, e0); e1 = fmaf(s1[4 * g + 1], kv.y, e1);
+                    e0 = fmaf(s1[4 * g + 2], kv.z, e0); e1 = fmaf(s1[4 * g + 3], kv.w, e1);
                 }
-                float dot = (d0 + d1) + (d2 + d3);
-                dot += __shfl_xor_sync(0xffffffffu, dot, 8);
-                dot += __shfl_xor_sync(0xffffffffu, dot, 16);
-                const float u = bsm[tt] * (vv - dot);
+                const float2 dot = reduce_pair<LN>(d0 + d1, e0 + e1, l);
+                const float beta = bsm[tt];
+                const float u0 = beta * (vv.x - dot.x), u1 = beta * (vv.y - dot.y);
 #pragma unroll
                 for (int g = 0; g < NG; ++g) {
                     const float4 kv = kk[LANES * g], qv = qq[LANES * g];
-                    s[4 * g] = fmaf(kv.x, u, s[4 * g]); s[4 * g + 1] = fmaf(kv.y, u, s[4 * g + 1]);
-                    s[4 * g + 2] = fmaf(kv.z, u, s[4 * g + 2]); s[4 * g + 3] = fmaf(kv.w, u, s[4 * g + 3]);
-                    a0 = fmaf(s[4 * g], qv.x, a0); a1 = fmaf(s[4 * g + 1], qv.y, a1);
-                    a2 = fmaf(s[4 * g + 2], qv.z, a2); a3 = fmaf(s[4 * g + 3], qv.w, a3);
+                    s0[4 * g] = fmaf(kv.x, u0, s0[4 * g]); s0[4 * g + 1] = fmaf(kv.y, u0, s0[4 * g + 1]);
+                    s0[4 * g + 2] = fmaf(kv.z, u0, s0[4 * g + 2]); s0[4 * g + 3] = fmaf(kv.w, u0, s0[4 * g + 3]);
+                    s1[4 * g] = fmaf(kv.x, u1, s1[4 * g]); s1[4 * g + 1] = fmaf(kv.y, u1, s1[4 * g + 1]);
+                    s1[4 * g + 2] = fmaf(kv.z, u1, s1[4 * g + 2]); s1[4 * g + 3] = fmaf(kv.w, u1, s1[4 * g + 3]);
+                    a0 = fmaf(s0[4 * g], qv.x, a0); a1 = fmaf(s0[4 * g + 1], qv.y, a1);
+                    a0 = fmaf(s0[4 * g + 2], qv.z, a0); a1 = fmaf(s0[4 * g + 3], qv.w, a1);
+                    b0 = fmaf(s1[4 * g], qv.x, b0); b1 = fmaf(s1[4 * g + 1], qv.y, b1);
+                    b0 = fmaf(s1[4 * g + 2], qv.z, b0); b1 = fmaf(s1[4 * g + 3], qv.w, b1);
                 }
             } else {
 #pragma unroll
                 for (int g = 0; g < NG; ++g) {
                     const float4 kv = kk[LANES * g], qv = qq[LANES * g];
-                    s[4 * g] = fmaf(dec, s[4 * g], kv.x * vv); s[4 * g + 1] = fmaf(dec, s[4 * g + 1], kv.y * vv);
-                    s[4 * g + 2] = fmaf(dec, s[4 * g + 2], kv.z * vv); s[4 * g + 3] = fmaf(dec, s[4 * g + 3], kv.w * vv);
-                    a0 = fmaf(s[4 * g], qv.x, a0); a1 = fmaf(s[4 * g + 1], qv.y, a1);
-                    a2 = fmaf(s[4 * g + 2], qv.z, a2); a3 = fmaf(s[4 * g + 3], qv.w, a3);
+                    s0[4 * g] = fmaf(dec, s0[4 * g], kv.x * vv.x); s0[4 * g + 1] = fmaf(dec, s0[4 * g + 1], kv.y * vv.x);
+                    s0[4 * g + 2] = fmaf(dec, s0[4 * g + 2], kv.z * vv.x); s0[4 * g + 3] = fmaf(dec, s0[4 * g + 3], kv.w * vv.x);
+                    s1[4 * g] = fmaf(dec, s1[4 * g], kv.x * vv.y); s1[4 * g + 1] = fmaf(dec, s1[4 * g + 1], kv.y * vv.y);
+                    s1[4 * g + 2] = fmaf(dec, s1[4 * g + 2], kv.z * vv.y); s1[4 * g + 3] = fmaf(dec, s1[4 * g + 3], kv.w * vv.y);
+                    a0 = fmaf(s0[4 * g], qv.x, a0); a1 = fmaf(s0[4 * g + 1], qv.y, a1);
+                    a0 = fmaf(s0[4 * g + 2], qv.z, a0); a1 = fmaf(s0[4 * g + 3], qv.w, a1);
+                    b0 = fmaf(s1[4 * g], qv.x, b0); b1 = fmaf(s1[4 * g + 1], qv.y, b1);
+                    b0 = fmaf(s1[4 * g + 2], qv.z, b0); b1 = fmaf(s1[4 * g + 3], qv.w, b1);
                 }
             }
-            float acc = (a0 + a1) + (a2 + a3);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 8);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 16);
-            if (l == 0 && colv) out[(size_t)(qs + t0 + tt) * H * V + (size_t)h * V + col] = acc;
+            // the read-out feeds nothing back: its partial sums wait in shared memory until the chunk's tokens are done
+            part[(tt * COLS + wcol) * (LANES + 1) + l] = a0 + a1;
+            part[(tt * COLS + wcol + 1) * (LANES + 1) + l] = b0 + b1;
         }
-        __syncthreads();                                       // the buffer is free for the chunk after the next
+        __syncthreads();                                       // partial sums complete; the staging buffer is free for the chunk after the next
+        for (int o = threadIdx.x; o < nt * COLS; o += SCAN_THREADS) {
+            const int tt = o / COLS, ci = o - tt * COLS;
+            const float* pp = part + o * (LANES + 1);
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < LANES; ++i) acc += pp[i];
+            if (col0 + ci < V) out[(size_t)(qs + t0 + tt) * H * V + (size_t)h * V + col0 + ci] = acc;
+        }
     }
 #pragma unroll
     for (int g = 0; g < NG; ++g)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int r = 4 * (l + LANES * g) + e;
-            if (r < D && colv) S[(size_t)r * V + col] = s[4 * g + e];
+            if (r < D && v0) S[(size_t)r * V + col] = s0[4 * g + e];
+            if (r < D && v1) S[(size_t)r * V + col + 1] = s1[4 * g + e];
         }
 }
 
 template <bool DELTA>
 int launch_scan(const float* prep, ScanLayout L, const float* decay, float* state, long long state_stride, float* out,
-                const int* seg_q_start, const int* seg_slot, int num_segs, int H, int KV, int D, int V, cudaStream_t stream) {
+                const int* seg_q_start, const int* seg_slot, int T_, int num_segs, int H, int KV, int D, int V, cudaStream_t stream) {
     if (num_segs == 0) return 0;
     if (D > 256 || H > 65535) return -2;
-    const int NG = D <= 32 ? 2 : D <= 64 ? 4 : D <= 128 ? 8 : 16;
-    const int per_token = (DELTA ? 3 : 2) * 16 * NG + COLS + 1;
-    const int TC = per_token * 16 * 2 * 4 <= 48 * 1024 ? 16 : per_token * 8 * 2 * 4 <= 48 * 1024 ? 8 : 4;
-    const size_t smem = 2 * (size_t)((TC * per_token + 3) & ~3) * sizeof(float);
+    // entries of many tokens: as many lanes per column pair as leave a lane one group of four rows (up to a warp);
+    // decode steps: 8 lanes, so that a warp moves the state in whole sectors
+    int LN = 8;
+    if (T_ > 4 * num_segs) LN = D > 64 ? 32 : D > 32 ? 16 : 8;
+    const int NG = (D + 4 * LN - 1) / (4 * LN);
+    const int COLS = cols_of(LN);
+    const int per_token = (DELTA ? 3 : 2) * 4 * LN * NG + COLS + 1;
+    const int per_chunk_token = 2 * per_token + COLS * (LN + 1);          // two staging buffers and the partial sums
+    const int TC = T_ <= 4 * num_segs ? 4 : per_chunk_token * 16 * 4 <= 96 * 1024 ? 16 : per_chunk_token * 8 * 4 <= 96 * 1024 ? 8 : 4;   // decode steps: small buffers, more blocks per SM
+    const size_t smem = (2 * (size_t)((TC * per_token + 3) & ~3) + (size_t)TC * COLS * (LN + 1)) * sizeof(float);
     // 16-byte copies need every piece on a 16-byte boundary: sizes and offsets in multiples of four floats
     const int vec = ((uintptr_t)prep % 16 == 0 && D % 4 == 0 && V % 4 == 0 && L.ld % 4 == 0 && L.q_off % 4 == 0 && L.k_off % 4 == 0 &&
                      L.v_off % 4 == 0 && (!DELTA || L.g_off % 4 == 0)) ? 1 : 0;
     dim3 grid(num_segs, H, (V + COLS - 1) / COLS);
-#define GO(N) state_scan_kernel<DELTA, N><<<grid, SCAN_THREADS, smem, stream>>>(prep, L, decay, state, state_stride, out, seg_q_start, seg_slot, H, KV, D, V, TC, vec)
-    if (NG == 2) GO(2); else if (NG == 4) GO(4); else if (NG == 8) GO(8); else GO(16);
+#define GO(LN_, N) do { \
+        auto kern = state_scan_kernel<DELTA, LN_, N>; \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); \
+        kern<<<grid, SCAN_THREADS, smem, stream>>>(prep, L, decay, state, state_stride, out, seg_q_start, seg_slot, H, KV, D, V, TC, vec); } while (0)
+    if (LN == 32) { if (NG == 1) GO(32, 1); else GO(32, 2); }
+    else if (LN == 16) GO(16, 1);
+    else { if (NG == 1) GO(8, 1); else if (NG == 2) GO(8, 2); else if (NG == 4) GO(8, 4); else GO(8, 8); }
 #undef GO
     return (int)cudaGetLastError();
 }
@@ -236,10 +284,12 @@ __global__ void delta_prepare_kernel(const T* __restrict__ p, int ldp, const T* 
                                      const float* __restrict__ state, long long state_stride, long long hist_off,
                                      float* __restrict__ out, int ldo, const int* __restrict__ token_seg,
                                      const int* __restrict__ seg_q_start, const int* __restrict__ seg_slot,
-                                     int H, int KV, int D, int V, int taps, float unit_eps) {
+                                     int H, int KV, int D, int V, int taps, float unit_eps, int T_, int toks) {
     __shared__ float scratch[32];
-    const int t = blockIdx.x, unit = blockIdx.y, seg = token_seg[t], qs = seg_q_start[seg], r = t - qs;
+    const int unit = blockIdx.y;
     const int C = 2 * KV * D + H * V;
+    for (int t = blockIdx.x * toks; t < min(T_, (int)(blockIdx.x + 1) * toks); ++t) {      // a block takes a unit of a few neighbouring tokens
+    const int seg = token_seg[t], qs = seg_q_start[seg], r = t - qs;
     const float* hist = state + (long long)seg_slot[seg] * state_stride + hist_off;
     float* o = out + (size_t)t * ldo;
     if (unit < 2 * KV) {
@@ -262,6 +312,7 @@ __global__ void delta_prepare_kernel(const T* __restrict__ p, int ldp, const T* 
         }
     } else {
         for (int h = threadIdx.x; h < H; h += 128) o[C + H * D + h] = sigmoidf(to_f32(p[(size_t)t * ldp + C + h]));
+    }
     }
 }
 
@@ -294,14 +345,14 @@ MI_EXPORT int mi_lightning_scan(const void* p, int ldp, float* prep, const float
     int err = (int)cudaGetLastError();
     if (err) return err;
     ScanLayout L{n, 0, H * D, 2 * H * D, 0, 0};
-    return launch_scan<false>(prep, L, decay, state, state_stride, out, seg_q_start, seg_slot, num_segs, H, H, D, V, stream);
+    return launch_scan<false>(prep, L, decay, state, state_stride, out, seg_q_start, seg_slot, T_, num_segs, H, H, D, V, stream);
 }
 
 MI_EXPORT int mi_delta_scan(const float* prep, int ld, float* state, long long state_stride, float* out, const int* seg_q_start,
-                            const int* seg_slot, int num_segs, int H, int KV, int D, int V, cudaStream_t stream) {
+                            const int* seg_slot, int T_, int num_segs, int H, int KV, int D, int V, cudaStream_t stream) {
     const int C = 2 * KV * D + H * V;
     ScanLayout L{ld, 0, KV * D, 2 * KV * D, C, C + H * D};
-    return launch_scan<true>(prep, L, nullptr, state, state_stride, out, seg_q_start, seg_slot, num_segs, H, KV, D, V, stream);
+    return launch_scan<true>(prep, L, nullptr, state, state_stride, out, seg_q_start, seg_slot, T_, num_segs, H, KV, D, V, stream);
 }
 
 MI_EXPORT int mi_delta_prepare(const void* p, int ldp, const void* a, int lda, const float* conv, const float* A_log, const float* dt_bias,
@@ -312,14 +363,15 @@ MI_EXPORT int mi_delta_prepare(const void* p, int ldp, const void* a, int lda, c
     const int C = 2 * KV * D + H * V;
     const int units = 2 * KV + 2 * H + 1;
     if (units > 65535) return -2;
-    dim3 pgrid(T_, units);
+    const int toks = T_ >= 1024 ? 8 : 1;
+    dim3 pgrid((T_ + toks - 1) / toks, units);
     if (dtype == MI_BF16)
         delta_prepare_kernel<__nv_bfloat16><<<pgrid, 128, 0, stream>>>((const __nv_bfloat16*)p, ldp, (const __nv_bfloat16*)a, lda, conv, A_log, dt_bias,
                                                                        state, state_stride, hist_off, out, ldo, token_seg, seg_q_start, seg_slot,
-                                                                       H, KV, D, V, taps, unit_eps);
+                                                                       H, KV, D, V, taps, unit_eps, T_, toks);
     else
         delta_prepare_kernel<float><<<pgrid, 128, 0, stream>>>((const float*)p, ldp, (const float*)a, lda, conv, A_log, dt_bias, state, state_stride,
-                                                               hist_off, out, ldo, token_seg, seg_q_start, seg_slot, H, KV, D, V, taps, unit_eps);
+                                                               hist_off, out, ldo, token_seg, seg_q_start, seg_slot, H, KV, D, V, taps, unit_eps, T_, toks);
     int err = (int)cudaGetLastError();
     if (err || taps <= 1) return err;
     dim3 grid(num_segs, (C + 255) / 256);

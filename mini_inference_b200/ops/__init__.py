@@ -683,7 +683,7 @@ class CudaOps:
         T = prep.shape[0]
         out = torch.empty((T, H * V), dtype=torch.float32, device=prep.device)
         _check(self.lib.mi_delta_scan(_p(prep), prep.stride(0), _p(state), _c.c_longlong(state.stride(0)), _p(out),
-                                      _p(batch.seg_q_start), _p(batch.seg_slot), batch.num_segs, H, KV, D, V, self._stream()),
+                                      _p(batch.seg_q_start), _p(batch.seg_slot), T, batch.num_segs, H, KV, D, V, self._stream()),
                "delta_scan")
         self.launches += 1
         return out
