@@ -286,7 +286,8 @@ def design_bench(args):
     from mini_inference_b200.engine.llm import LLM
     from mini_inference_b200.ops import get_ops
 
-    pk, vocab, out = peaks(), 65536, {"design": "naditar", "peaks": pk, "sizes": {}}
+    pk, vocab = peaks(), 65536
+    out = {"design": "naditar", "peaks": pk, "sizes": {}}
     for size in args.design_sizes.split(","):
         res = {}
         for name, cfg in (("naditar", microbench.naditar_config(size, args.design_layers, vocab)),

@@ -119,6 +119,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(
     const bool v0 = col < V, v1 = col + 1 < V;
     for (int i = threadIdx.x; i < 2 * buf_stride; i += SCAN_THREADS) sm[i] = 0.f;       // the pads beyond D (and V) stay zero
     float* S = state + (long long)slot * state_stride + (long long)h * D * V;
+    __syncthreads();
+    // the first chunk's copies start before the state is fetched, so that the two waits for global memory overlap
+    const int chunks = (n + TC - 1) / TC;
+    stage_chunk<DELTA, COLS>(sm, Dp, TC, prep, L, qs, min(TC, n), h, kvh, D, V, col0, vec != 0);
+    cp_commit();
     float s0[4 * NG], s1[4 * NG];
 #pragma unroll
     for (int g = 0; g < NG; ++g)
@@ -129,10 +134,6 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(
             s1[4 * g + e] = (r < D && v1) ? S[(size_t)r * V + col + 1] : 0.f;
         }
     const float dec = DELTA ? 0.f : decay[h];
-    __syncthreads();
-    const int chunks = (n + TC - 1) / TC;
-    stage_chunk<DELTA, COLS>(sm, Dp, TC, prep, L, qs, min(TC, n), h, kvh, D, V, col0, vec != 0);
-    cp_commit();
     for (int c = 0; c < chunks; ++c) {
         const int t0 = c * TC, nt = min(TC, n - t0);
         if (c + 1 < chunks) {
