@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(
     __syncthreads();
     // the first chunk's copies start before the state is fetched, so that the two waits for global memory overlap
     const int chunks = (n + TC - 1) / TC;
-    stage_chunk<DELTA, COLS>(sm, Dp, TC, prep, L, qs, min(TC, n), h, kvh, D, V, col0, vec != 0);
+    stage_chunk<DELTA, COLS>(sm, Dp, TC, prep, L, qs, min(TC, n), h, kvh, D, V, col0, (vec & 1) != 0);
     cp_commit();
     float s0[4 * NG], s1[4 * NG];
 #pragma unroll
@@ -130,14 +130,19 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int r = 4 * (l + LANES * g) + e;
-            s0[4 * g + e] = (r < D && v0) ? S[(size_t)r * V + col] : 0.f;
-            s1[4 * g + e] = (r < D && v1) ? S[(size_t)r * V + col + 1] : 0.f;
+            if (vec & 2) {                                     // even V and slot size: a pair of columns is one 8-byte access
+                const float2 t = (r < D && v0) ? *reinterpret_cast<const float2*>(S + (size_t)r * V + col) : make_float2(0.f, 0.f);
+                s0[4 * g + e] = t.x; s1[4 * g + e] = t.y;
+            } else {
+                s0[4 * g + e] = (r < D && v0) ? S[(size_t)r * V + col] : 0.f;
+                s1[4 * g + e] = (r < D && v1) ? S[(size_t)r * V + col + 1] : 0.f;
+            }
         }
     const float dec = DELTA ? 0.f : decay[h];
     for (int c = 0; c < chunks; ++c) {
         const int t0 = c * TC, nt = min(TC, n - t0);
         if (c + 1 < chunks) {
-            stage_chunk<DELTA, COLS>(sm + ((c + 1) & 1) * buf_stride, Dp, TC, prep, L, qs + t0 + TC, min(TC, n - t0 - TC), h, kvh, D, V, col0, vec != 0);
+            stage_chunk<DELTA, COLS>(sm + ((c + 1) & 1) * buf_stride, Dp, TC, prep, L, qs + t0 + TC, min(TC, n - t0 - TC), h, kvh, D, V, col0, (vec & 1) != 0);
             cp_commit();
             cp_wait<1>();
         } else {
@@ -217,8 +222,12 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int r = 4 * (l + LANES * g) + e;
-            if (r < D && v0) S[(size_t)r * V + col] = s0[4 * g + e];
-            if (r < D && v1) S[(size_t)r * V + col + 1] = s1[4 * g + e];
+            if (vec & 2) {
+                if (r < D && v0) *reinterpret_cast<float2*>(S + (size_t)r * V + col) = make_float2(s0[4 * g + e], s1[4 * g + e]);
+            } else {
+                if (r < D && v0) S[(size_t)r * V + col] = s0[4 * g + e];
+                if (r < D && v1) S[(size_t)r * V + col + 1] = s1[4 * g + e];
+            }
         }
 }
 
@@ -238,8 +247,9 @@ int launch_scan(const float* prep, ScanLayout L, const float* decay, float* stat
     const int TC = T_ <= 4 * num_segs ? 4 : per_chunk_token * 16 * 4 <= 96 * 1024 ? 16 : per_chunk_token * 8 * 4 <= 96 * 1024 ? 8 : 4;   // decode steps: small buffers, more blocks per SM
     const size_t smem = (2 * (size_t)((TC * per_token + 3) & ~3) + (size_t)TC * COLS * (LN + 1)) * sizeof(float);
     // 16-byte copies need every piece on a 16-byte boundary: sizes and offsets in multiples of four floats
-    const int vec = ((uintptr_t)prep % 16 == 0 && D % 4 == 0 && V % 4 == 0 && L.ld % 4 == 0 && L.q_off % 4 == 0 && L.k_off % 4 == 0 &&
-                     L.v_off % 4 == 0 && (!DELTA || L.g_off % 4 == 0)) ? 1 : 0;
+    const int vec = (((uintptr_t)prep % 16 == 0 && D % 4 == 0 && V % 4 == 0 && L.ld % 4 == 0 && L.q_off % 4 == 0 && L.k_off % 4 == 0 &&
+                     L.v_off % 4 == 0 && (!DELTA || L.g_off % 4 == 0)) ? 1 : 0)
+                  | ((V % 2 == 0 && state_stride % 2 == 0 && (uintptr_t)state % 8 == 0) ? 2 : 0);      // bit 1: the state in 8-byte pairs
     dim3 grid(num_segs, H, (V + COLS - 1) / COLS);
 #define GO(LN_, N) do { \
         auto kern = state_scan_kernel<DELTA, LN_, N>; \

@@ -89,7 +89,7 @@ class ChannelDeltaRule(Part):
         # that is to be filled with random weights names them
         self.a_rank, self.g_rank = int(g("decay_rank", -1)), int(g("gate_rank", -1))
         self.C = 2 * self.KV * self.D + self.H * self.V             # channels that pass the short convolution
-        self.proj = self.a2 = self.g2 = self.o = self.conv = self.A_log = self.dt_bias = self.norm = None
+        self.proj = self.ag2 = self.o = self.conv = self.A_log = self.dt_bias = self.norm = None
 
     def weight_specs(self):
         H, KV, D, V, hid, taps = self.H, self.KV, self.D, self.V, self.hidden, self.taps
@@ -107,10 +107,13 @@ class ChannelDeltaRule(Part):
 
     def load(self, tensors, dtype, device):
         a1, g1 = tensors.pop("a1"), tensors.pop("g1")
-        self.a2, self.g2 = tensors.pop("a2"), tensors.pop("g2")
+        a2, g2 = tensors.pop("a2"), tensors.pop("g2")
         self.a_rank, self.g_rank = a1.shape[0], g1.shape[0]
-        if self.a2.shape[1] != self.a_rank or self.g2.shape[1] != self.g_rank:
+        if a2.shape[1] != self.a_rank or g2.shape[1] != self.g_rank:
             raise ValueError("the two halves of a low-rank projection disagree about its rank")
+        # the second halves of both low-rank projections as ONE product: [a2 0; 0 g2] on the neighbouring columns a1 | g1
+        # of the first product (the zero blocks add nothing to any sum)
+        self.ag2 = torch.block_diag(a2, g2).contiguous()
         # one product for everything that reads the mixer's input: q | k | v | b | a1 | g1
         self.proj = torch.cat([tensors.pop("q"), tensors.pop("k"), tensors.pop("v"), tensors.pop("b"), a1, g1], dim=0).contiguous()
         self.conv = torch.cat([tensors.pop("q.conv"), tensors.pop("k.conv"), tensors.pop("v.conv")], dim=0).float().contiguous()
@@ -136,10 +139,8 @@ class ChannelDeltaRule(Part):
     def forward_open(self, h, ctx, cache, position, owns_cache=True):
         ops, H, KV, D, V, C = ctx.ops, self.H, self.KV, self.D, self.V, self.C
         p = ops.linear(h, self.proj)
-        a_in = p[:, C + H:C + H + self.a_rank]
-        g_in = p[:, C + H + self.a_rank:]
-        a = ops.linear(a_in, self.a2)                               # [T, H D]
-        gate = ops.linear(g_in, self.g2)                            # [T, H V]
+        ag = ops.linear(p[:, C + H:], self.ag2)                     # [T, H D + H V]: decay logits | gate logits
+        a, gate = ag[:, :H * D], ag[:, H * D:]
         prep = ops.delta_prepare(p, a, self.conv, self.A_log, self.dt_bias, H, KV, D, V, self.taps, self.unit_eps,
                                  cache.state, ctx.batch)            # float32 q | k | v | beta | g per token; conv tail -> state
         o = ops.delta_scan(prep, H, KV, D, V, cache.state, ctx.batch)                   # float32 [T, H V]
