@@ -230,6 +230,10 @@ SINGLE = {
     "channel_delta_taps4": config(36, 67, [delta(2, 2, 20, 33, 4)]),
     "latent": config(40, 71, [latent(3, 8, 6, 10, 12)]),
     "latent_part_rotated": config(40, 71, [latent(2, 4, 12, 6, 20, dims=8, base=100.0)]),
+    # sizes that put every view of a fused product on an odd offset and every row on an odd length
+    "lightning_odd": config(27, 53, [light(3, 5, 7, [0.4, 0.8, 0.95])]),
+    "channel_delta_odd": config(27, 53, [delta(3, 1, 9, 6, 3, rank=3)]),
+    "latent_odd": config(27, 53, [latent(3, 5, 4, 3, 7, dims=2)]),
 }
 
 
@@ -447,16 +451,17 @@ def test_mixed_batches_on_gpu(dirs, name, dtype):
 
 
 @gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", sorted(SINGLE))
-def test_each_mechanism_alone_on_gpu(tmp_path, name):
+def test_each_mechanism_alone_on_gpu(tmp_path, name, dtype):
     cfg = SINGLE[name]
     d = write_random_model(cfg, str(tmp_path), seed=3, std=0.3, norm_init="uniform")
     ids = tokens(cfg["vocab"], 150, seed=1)
     want = plain_logits(d, ids)
-    runner = engine(d, 16, 16, "float32", "cuda:0")
-    assert err(feed(runner, "w", ids, [150]), want) < 1e-4
-    assert err(feed(runner, "d", ids, [110] + [1] * 40), want) < 1e-4
-    assert err(feed(runner, "p", ids, [2, 64, 3, 17, 2, 33, 29]), want) < 1e-4
+    runner = engine(d, 16, 16, dtype, "cuda:0")
+    assert err(feed(runner, "w", ids, [150]), want) < TOL[dtype]
+    assert err(feed(runner, "d", ids, [110] + [1] * 40), want) < TOL[dtype]
+    assert err(feed(runner, "p", ids, [2, 64, 3, 17, 2, 33, 29]), want) < TOL[dtype]
 
 
 @gpu
