@@ -276,10 +276,13 @@ def bench_design(args, ops, peak, out=print):
     cache = torch.randn(4, pages + 1, 1, ps, C + R, device="cuda", dtype=bf)
     q = torch.randn(T, LH, C + R, device="cuda", dtype=bf)
     pairs = T * (T + 1) / 2
-    for label, tc, bound in (("float32 weights", False, "fma"), ("tensor cores", True, "bf16")):
-        ops.latent_tc = tc
-        us = timed(lambda i: ops.latent_attention(q, cache[i % 4], meta, LH, C, R, 0.1), max(3, it // (1 if tc else 10)))
-        line(f"latent attention, {label}", f"prompt T={T} heads={LH} rows {C}+{R}", us, 2.0 * LH * (2 * C + R) * pairs, bound)
+    # default: mma.sync kernels with every softmax weight as two bfloat16 numbers; MI_LATENT_TC=1: tcgen05 / mma kernels, bfloat16 weights;
+    # the float32 kernels of csrc/attention_latent.cu (any row size) are timed on a shorter prompt
+    for label, tc, fast in (("split weights", False, True), ("bf16 weights", True, True), ("float32 kernel", False, False)):
+        ops.latent_tc, ops.fast_attention = tc, fast
+        us = timed(lambda i: ops.latent_attention(q, cache[i % 4], meta, LH, C, R, 0.1), it if fast else 3)
+        line(f"latent attention, {label}", f"prompt T={T} heads={LH} rows {C}+{R}", us, 2.0 * LH * (2 * C + R) * pairs, "bf16" if fast else "fma")
+    ops.fast_attention = True
     kv = torch.randn(4, 2, pages + 1, KV, ps, 128, device="cuda", dtype=bf)
     qq = torch.randn(T, H * 128, device="cuda", dtype=bf)
     meta.table_rows = None
@@ -297,10 +300,11 @@ def bench_design(args, ops, peak, out=print):
                                      prefill_tiles=torch.zeros((0, 2), dtype=torch.int32, device="cuda"), prefill_tiles2=None, max_kv_len=ctx, num_tokens=B)
         cache = torch.randn(layers, B * pages + 1, 1, ps, C + R, device="cuda", dtype=bf)
         q = torch.randn(B, LH, C + R, device="cuda", dtype=bf)
-        for label, tc in (("float32 weights", False), ("tensor cores", True)):
-            ops.latent_tc = tc
-            us = timed(lambda i: ops.latent_attention(q, cache[i % layers], meta, LH, C, R, 0.1), it)
+        for label, tc, fast in (("split weights", False, True), ("bf16 weights", True, True), ("float32 kernel", False, False)):
+            ops.latent_tc, ops.fast_attention = tc, fast
+            us = timed(lambda i: ops.latent_attention(q, cache[i % layers], meta, LH, C, R, 0.1), it if fast else 3)
             line(f"latent attention, {label}", f"decode B={B} ctx={ctx} heads={LH} rows {C}+{R}", us, B * ctx * (C + R) * 2.0, "hbm")
+        ops.fast_attention = True
         del cache
         layers = max(2, (512 << 20) // (B * pages * ps * KV * 128 * 4) + 1)
         kv = torch.randn(layers, 2, B * pages + 1, KV, ps, 128, device="cuda", dtype=bf)
@@ -309,7 +313,7 @@ def bench_design(args, ops, peak, out=print):
         us = timed(lambda i: ops.paged_attention(qq, kv[i % layers, 0], kv[i % layers, 1], meta, H, KV, 128, 0.1, None), it)
         line("  Qwen3: attention", f"decode B={B} ctx={ctx} heads={H}/{KV} D=128", us, B * ctx * KV * 128 * 4.0, "hbm")
         del kv
-    ops.latent_tc = False
+    ops.latent_tc, ops.fast_attention = False, True
     ops.check_errors()
     return rows
 

@@ -76,7 +76,9 @@ constexpr int DEC_WARPS_ALONE = 8; // warps of a block that has its SM to itself
 //               swizzle spreads the 8 keys of a quarter-warp over the banks; the score product takes its 16-byte
 //               pieces in the order 2c + (j & 1) so that neighbouring lanes also differ in the column).  More bytes
 //               in flight per SM at no register cost.
-template <int D, bool BULK, int WARPS>
+// SPLIT: every softmax weight enters the P V product as two bfloat16 numbers, its rounding and what the rounding left behind
+// (16 mantissa bits in all, summed in float32), for designs that want their attention weights in more than 16-bit precision.
+template <int D, bool BULK, int WARPS, bool SPLIT = false>
 __global__ void __launch_bounds__(WARPS * 32, WARPS > DEC_WARPS ? 1 : BULK ? 2 : 3)
 attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                        const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
@@ -266,7 +268,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
         const float al0 = exp2f(m0 - n0), al1 = exp2f(m1 - n1);
         m0 = n0; m1 = n1;
         l0 *= al0; l1 *= al1;
-        uint32_t pa[4];
+        uint32_t pa[4], pr[4] = {0u, 0u, 0u, 0u};
         {
             float p[2][4];
 #pragma unroll
@@ -278,6 +280,14 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
             }
             pa[0] = pack_bf16(p[0][0], p[0][1]); pa[1] = pack_bf16(p[0][2], p[0][3]);
             pa[2] = pack_bf16(p[1][0], p[1][1]); pa[3] = pack_bf16(p[1][2], p[1][3]);
+            if (SPLIT) {
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) p[nt][e] -= __bfloat162float(__float2bfloat16_rn(p[nt][e]));
+                pr[0] = pack_bf16(p[0][0], p[0][1]); pr[1] = pack_bf16(p[0][2], p[0][3]);
+                pr[2] = pack_bf16(p[1][0], p[1][1]); pr[3] = pack_bf16(p[1][2], p[1][3]);
+            }
         }
         // O += P V; tile t of half hb: column g is d = 64 hb + 8 g + t
 #pragma unroll
@@ -294,6 +304,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
                 float (&acc)[4] = o[hb * 8 + t];
                 acc[0] *= al0; acc[1] *= al0; acc[2] *= al1; acc[3] *= al1;
                 mma_bf16_16816(acc, pa, vb0, vb1);
+                if (SPLIT) mma_bf16_16816(acc, pr, vb0, vb1);
             }
         }
         if (!BULK && blk + WARPS < b1) load_v(blk + WARPS);
@@ -512,12 +523,13 @@ MI_EXPORT int mi_attn_decode_cluster_fit(int D, int splits) {
 // the device) and entry i reads row table_rows[i]; null: entry i reads row i.  cluster_merge != 0: with 2..8 splits the
 // splits of a (request, kv head) are launched as one thread-block cluster and merged through distributed shared memory
 // (o_part, lse_part, merge_counters unused).
-MI_EXPORT int mi_attn_decode_mma_rows(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
-                                      float* o_part, float* lse_part, const int* decode_segs, int num_decode,
-                                      const int* seg_q_start, const int* seg_kv_len, const int* block_table,
-                                      const int* table_rows, int table_stride, int H, int KV, int D, int ps, int splits,
-                                      float scale, int window, int* merge_counters, int* error_word, int cache_pages,
-                                      int cluster_merge, cudaStream_t stream) {
+template <bool SPLIT>
+static int decode_mma_rows_launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                  float* o_part, float* lse_part, const int* decode_segs, int num_decode,
+                                  const int* seg_q_start, const int* seg_kv_len, const int* block_table,
+                                  const int* table_rows, int table_stride, int H, int KV, int D, int ps, int splits,
+                                  float scale, int window, int* merge_counters, int* error_word, int cache_pages,
+                                  int cluster_merge, cudaStream_t stream) {
     if (num_decode == 0) return 0;
     if ((D != 64 && D != 128) || H % KV || H / KV > 16 || ps % 16 || q_stride % 8) return -2;
     dim3 grid(num_decode, KV, splits);
@@ -546,7 +558,7 @@ MI_EXPORT int mi_attn_decode_mma_rows(const void* q, int q_stride, const void* k
 #define LAUNCH(DD, BB, WW) do { \
         static bool configured = false; \
         if (!configured && smem > 48 * 1024) { \
-            cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<DD, BB, WW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<DD, BB, WW, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return (int)e; \
             configured = true; \
         } \
@@ -564,14 +576,14 @@ MI_EXPORT int mi_attn_decode_mma_rows(const void* q, int q_stride, const void* k
             if (fit[splits] == 0) { \
                 cfg.attrs = attr; cfg.numAttrs = 1; \
                 int n = 0; \
-                if (cudaOccupancyMaxActiveClusters(&n, attn_decode_mma_kernel<DD, BB, WW>, &cfg) != cudaSuccess || n < 1) n = -1; \
+                if (cudaOccupancyMaxActiveClusters(&n, attn_decode_mma_kernel<DD, BB, WW, SPLIT>, &cfg) != cudaSuccess || n < 1) n = -1; \
                 fit[splits] = n; \
             } \
             /* (with a margin: blocks of the kernels before and after share the SMs for a moment) */ \
             if (fit[splits] < 0 || (long long)num_decode * KV * 100 > (long long)fit[splits] * 92) use_cluster = 0; \
         } \
         cfg.attrs = use_cluster ? attr : attr + 1; cfg.numAttrs = use_cluster ? 2 : 1; \
-        return (int)cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<DD, BB, WW>, kmap, vmap, \
+        return (int)cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<DD, BB, WW, SPLIT>, kmap, vmap, \
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
             (__nv_bfloat16*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, block_table, table_rows, \
             table_stride, H, KV, ps, scale_log2, window, merge_counters, error_word, use_cluster); } while (0)
@@ -580,3 +592,25 @@ MI_EXPORT int mi_attn_decode_mma_rows(const void* q, int q_stride, const void* k
 #undef LAUNCH
     return (int)cudaGetLastError();
 }
+
+#define DECODE_ROWS_ARGS q, q_stride, k_cache, v_cache, out, o_part, lse_part, decode_segs, num_decode, seg_q_start, seg_kv_len, block_table, \
+        table_rows, table_stride, H, KV, D, ps, splits, scale, window, merge_counters, error_word, cache_pages, cluster_merge, stream
+MI_EXPORT int mi_attn_decode_mma_rows(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                      float* o_part, float* lse_part, const int* decode_segs, int num_decode,
+                                      const int* seg_q_start, const int* seg_kv_len, const int* block_table,
+                                      const int* table_rows, int table_stride, int H, int KV, int D, int ps, int splits,
+                                      float scale, int window, int* merge_counters, int* error_word, int cache_pages,
+                                      int cluster_merge, cudaStream_t stream) {
+    return decode_mma_rows_launch<false>(DECODE_ROWS_ARGS);
+}
+
+// The same with every softmax weight split into two bfloat16 numbers for the P V product (see SPLIT above).
+MI_EXPORT int mi_attn_decode_mma_rows_split(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                            float* o_part, float* lse_part, const int* decode_segs, int num_decode,
+                                            const int* seg_q_start, const int* seg_kv_len, const int* block_table,
+                                            const int* table_rows, int table_stride, int H, int KV, int D, int ps, int splits,
+                                            float scale, int window, int* merge_counters, int* error_word, int cache_pages,
+                                            int cluster_merge, cudaStream_t stream) {
+    return decode_mma_rows_launch<true>(DECODE_ROWS_ARGS);
+}
+#undef DECODE_ROWS_ARGS

@@ -6,7 +6,8 @@
 // attention kernels take (C + R of 64 or 128, bfloat16) are sent there by the kernel namespace instead.
 //
 // Cache layout: [pages, 1, page_size, C + R]; the row of key j of a request is at (table[j / ps] * ps + j % ps) * (C + R).
-// Output layout: [H, T, C] (what the per-head value up-projection reads as a batch of matrices).
+// Output: element d of head h of token t goes to out[h * out_hs + t * out_ts + d] ([H, T, C]: out_hs = T C, out_ts = C, what the
+// per-head value up-projection reads as a batch of matrices; or a [T, H, C + R] buffer shared with another kernel's output).
 #include "common.cuh"
 #include <math.h>
 
@@ -119,7 +120,7 @@ template <typename T, int NV>
 __global__ void latent_prefill_kernel(const T* __restrict__ q, const T* __restrict__ cache, T* __restrict__ out,
                                       const int* __restrict__ tiles, const int* __restrict__ seg_q_start,
                                       const int* __restrict__ seg_pos0, const int* __restrict__ block_table,
-                                      const int* __restrict__ table_rows, int table_stride, int T_, int H, int Dk, int Dv, int ps,
+                                      const int* __restrict__ table_rows, int table_stride, long long out_hs, long long out_ts, int H, int Dk, int Dv, int ps,
                                       int tile_rows, float scale, int vec) {
     extern __shared__ float q_sm[];                      // [WARPS, Dk]
     const int seg = tiles[2 * blockIdx.x], r0 = tiles[2 * blockIdx.x + 1];
@@ -138,7 +139,7 @@ __global__ void latent_prefill_kernel(const T* __restrict__ q, const T* __restri
 #pragma unroll
         for (int k = 0; k < NV; ++k) acc[k] = 0.f;
         attend_rows<T, NV>(q_s, cache, table_row, Dk, Dv, ps, vec != 0, 0, pq + 1, m, l, acc);
-        T* orow = out + ((size_t)h * T_ + tok) * Dv;
+        T* orow = out + h * out_hs + tok * out_ts;
 #pragma unroll
         for (int k = 0; k < NV; ++k) {
             const int d = lane + 32 * k;
@@ -155,7 +156,7 @@ __global__ void latent_decode_kernel(const T* __restrict__ q, const T* __restric
                                      float* __restrict__ o_part, float* __restrict__ lse_part, const int* __restrict__ decode_segs,
                                      const int* __restrict__ seg_q_start, const int* __restrict__ seg_kv_len,
                                      const int* __restrict__ block_table, const int* __restrict__ table_rows, int table_stride,
-                                     int T_, int H, int Dk, int Dv, int ps, float scale, int vec) {
+                                     long long out_hs, long long out_ts, int H, int Dk, int Dv, int ps, float scale, int vec) {
     extern __shared__ float q_sm[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int h = blockIdx.y * WARPS + warp;
@@ -176,7 +177,7 @@ __global__ void latent_decode_kernel(const T* __restrict__ q, const T* __restric
         attend_rows<T, NV>(q_s, cache, block_table + (size_t)table_rows[seg] * table_stride, Dk, Dv, ps, vec != 0, lo, hi, m, l, acc);
     const float inv = l > 0.f ? 1.f / l : 0.f;                  // empty piece: output 0, lse -inf
     if (S == 1) {
-        T* orow = out + ((size_t)h * T_ + tok) * Dv;
+        T* orow = out + h * out_hs + tok * out_ts;
 #pragma unroll
         for (int k = 0; k < NV; ++k) { const int d = lane + 32 * k; if (d < Dv) orow[d] = from_f32<T>(acc[k] * inv); }
     } else {
@@ -191,7 +192,7 @@ __global__ void latent_decode_kernel(const T* __restrict__ q, const T* __restric
 // out = sum_s e^(lse_s - max) o_s / sum_s e^(lse_s - max), in split order
 template <typename T>
 __global__ void latent_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ lse_part, T* __restrict__ out,
-                                    const int* __restrict__ decode_segs, const int* __restrict__ seg_q_start, int T_, int H, int Dv, int S) {
+                                    const int* __restrict__ decode_segs, const int* __restrict__ seg_q_start, long long out_hs, long long out_ts, int H, int Dv, int S) {
     const int i = blockIdx.x, h = blockIdx.y;
     const int tok = seg_q_start[decode_segs[i]];
     const size_t base = ((size_t)i * H + h) * S;
@@ -202,7 +203,7 @@ __global__ void latent_merge_kernel(const float* __restrict__ o_part, const floa
     for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
         float num = 0.f;
         for (int s = 0; s < S; ++s) num += expf(lse_part[base + s] - mx) * o_part[(base + s) * Dv + d];
-        out[((size_t)h * T_ + tok) * Dv + d] = from_f32<T>(num / den);
+        out[h * out_hs + tok * out_ts + d] = from_f32<T>(num / den);
     }
 }
 
@@ -224,8 +225,8 @@ MI_EXPORT int mi_latent_prepare(const void* p, int ldp, const void* q_abs, void*
 #define LATENT_PICK_NV(CALL) do { if (Dv <= 64) { CALL(2); } else if (Dv <= 128) { CALL(4); } else if (Dv <= 256) { CALL(8); } else { CALL(16); } } while (0)
 
 MI_EXPORT int mi_latent_prefill(const void* q, const void* cache, void* out, const int* tiles, int num_tiles, const int* seg_q_start,
-                                const int* seg_pos0, const int* block_table, const int* table_rows, int table_stride, int T_, int H,
-                                int C, int R, int ps, int tile_rows, float scale, int dtype, cudaStream_t stream) {
+                                const int* seg_pos0, const int* block_table, const int* table_rows, int table_stride, long long out_hs,
+                                long long out_ts, int H, int C, int R, int ps, int tile_rows, float scale, int dtype, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     const int Dk = C + R, Dv = C;
     if (Dv > 512 || Dk > 2048 || H > 65535) return -2;
@@ -235,9 +236,9 @@ MI_EXPORT int mi_latent_prefill(const void* q, const void* cache, void* out, con
     dim3 grid(num_tiles, H);
 #define CALL(NV) do { \
         if (dtype == MI_BF16) latent_prefill_kernel<__nv_bfloat16, NV><<<grid, WARPS * 32, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, \
-            (__nv_bfloat16*)out, tiles, seg_q_start, seg_pos0, block_table, table_rows, table_stride, T_, H, Dk, Dv, ps, tile_rows, scale, vec); \
+            (__nv_bfloat16*)out, tiles, seg_q_start, seg_pos0, block_table, table_rows, table_stride, out_hs, out_ts, H, Dk, Dv, ps, tile_rows, scale, vec); \
         else latent_prefill_kernel<float, NV><<<grid, WARPS * 32, smem, stream>>>((const float*)q, (const float*)cache, (float*)out, tiles, seg_q_start, \
-            seg_pos0, block_table, table_rows, table_stride, T_, H, Dk, Dv, ps, tile_rows, scale, vec); } while (0)
+            seg_pos0, block_table, table_rows, table_stride, out_hs, out_ts, H, Dk, Dv, ps, tile_rows, scale, vec); } while (0)
     LATENT_PICK_NV(CALL);
 #undef CALL
     return (int)cudaGetLastError();
@@ -245,8 +246,8 @@ MI_EXPORT int mi_latent_prefill(const void* q, const void* cache, void* out, con
 
 MI_EXPORT int mi_latent_decode(const void* q, const void* cache, void* out, float* o_part, float* lse_part, const int* decode_segs,
                                int num_decode, const int* seg_q_start, const int* seg_kv_len, const int* block_table,
-                               const int* table_rows, int table_stride, int T_, int H, int C, int R, int ps, int splits, float scale,
-                               int dtype, cudaStream_t stream) {
+                               const int* table_rows, int table_stride, long long out_hs, long long out_ts, int H, int C, int R, int ps, int splits,
+                               float scale, int dtype, cudaStream_t stream) {
     if (num_decode == 0) return 0;
     const int Dk = C + R, Dv = C;
     if (Dv > 512 || Dk > 2048 || H > 65535 * WARPS) return -2;
@@ -256,17 +257,17 @@ MI_EXPORT int mi_latent_decode(const void* q, const void* cache, void* out, floa
     dim3 grid(num_decode, (H + WARPS - 1) / WARPS, splits);
 #define CALL(NV) do { \
         if (dtype == MI_BF16) latent_decode_kernel<__nv_bfloat16, NV><<<grid, WARPS * 32, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, \
-            (__nv_bfloat16*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, block_table, table_rows, table_stride, T_, H, Dk, Dv, ps, scale, vec); \
+            (__nv_bfloat16*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, block_table, table_rows, table_stride, out_hs, out_ts, H, Dk, Dv, ps, scale, vec); \
         else latent_decode_kernel<float, NV><<<grid, WARPS * 32, smem, stream>>>((const float*)q, (const float*)cache, (float*)out, o_part, lse_part, \
-            decode_segs, seg_q_start, seg_kv_len, block_table, table_rows, table_stride, T_, H, Dk, Dv, ps, scale, vec); } while (0)
+            decode_segs, seg_q_start, seg_kv_len, block_table, table_rows, table_stride, out_hs, out_ts, H, Dk, Dv, ps, scale, vec); } while (0)
     LATENT_PICK_NV(CALL);
 #undef CALL
     int err = (int)cudaGetLastError();
     if (err || splits == 1) return err;
     dim3 mgrid(num_decode, H);
     if (dtype == MI_BF16)
-        latent_merge_kernel<__nv_bfloat16><<<mgrid, 128, 0, stream>>>(o_part, lse_part, (__nv_bfloat16*)out, decode_segs, seg_q_start, T_, H, Dv, splits);
+        latent_merge_kernel<__nv_bfloat16><<<mgrid, 128, 0, stream>>>(o_part, lse_part, (__nv_bfloat16*)out, decode_segs, seg_q_start, out_hs, out_ts, H, Dv, splits);
     else
-        latent_merge_kernel<float><<<mgrid, 128, 0, stream>>>(o_part, lse_part, (float*)out, decode_segs, seg_q_start, T_, H, Dv, splits);
+        latent_merge_kernel<float><<<mgrid, 128, 0, stream>>>(o_part, lse_part, (float*)out, decode_segs, seg_q_start, out_hs, out_ts, H, Dv, splits);
     return (int)cudaGetLastError();
 }

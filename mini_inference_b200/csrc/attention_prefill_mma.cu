@@ -50,7 +50,12 @@ template <int D> __device__ __forceinline__ uint32_t swz(int row, int chunk) {
     return (uint32_t)(row * D * 2 + ((chunk ^ (row & 7)) << 4));
 }
 
-template <int D>
+// the part of a softmax weight that its bfloat16 rounding leaves behind
+__device__ __forceinline__ float bf16_rest(float x) { return x - __bfloat162float(__float2bfloat16_rn(x)); }
+
+// SPLIT: every softmax weight enters the P V product as TWO bfloat16 numbers, its rounding and what the rounding left behind
+// (16 mantissa bits in all, summed in float32), for designs that want their attention weights in more than 16-bit precision.
+template <int D, bool SPLIT>
 __global__ void __launch_bounds__(PF_WARPS * 32, 3)
 attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
                         const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
@@ -183,6 +188,12 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
             uint32_t pa[4];
             pa[0] = pack2(s[2 * kk][0], s[2 * kk][1]); pa[1] = pack2(s[2 * kk][2], s[2 * kk][3]);
             pa[2] = pack2(s[2 * kk + 1][0], s[2 * kk + 1][1]); pa[3] = pack2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+            uint32_t pr[4] = {0u, 0u, 0u, 0u};
+            if (SPLIT) {
+                pr[0] = pack2(bf16_rest(s[2 * kk][0]), bf16_rest(s[2 * kk][1])); pr[1] = pack2(bf16_rest(s[2 * kk][2]), bf16_rest(s[2 * kk][3]));
+                pr[2] = pack2(bf16_rest(s[2 * kk + 1][0]), bf16_rest(s[2 * kk + 1][1]));
+                pr[3] = pack2(bf16_rest(s[2 * kk + 1][2]), bf16_rest(s[2 * kk + 1][3]));
+            }
 #pragma unroll
             for (int dp = 0; dp < DT / 2; ++dp) {
                 uint32_t b[4];
@@ -190,6 +201,10 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                 ldmatrix_x4_trans(b, vbuf + swz<D>(kk * 16 + (mi & 1) * 8 + (lane & 7), 2 * dp + (mi >> 1)));
                 mma16816(o[2 * dp], pa, b[0], b[1]);
                 mma16816(o[2 * dp + 1], pa, b[2], b[3]);
+                if (SPLIT) {
+                    mma16816(o[2 * dp], pr, b[0], b[1]);
+                    mma16816(o[2 * dp + 1], pr, b[2], b[3]);
+                }
             }
         }
         cp_async_wait<0>();
@@ -211,10 +226,11 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
 
 }  // namespace
 
-MI_EXPORT int mi_attn_prefill_mma(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
-                                  const int* tiles, int num_tiles, const int* seg_q_start, const int* seg_pos0,
-                                  const int* block_table, const int* table_rows, int table_stride, int H, int KV, int D, int ps,
-                                  int tile_rows, float scale, int window, cudaStream_t stream) {
+template <bool SPLIT>
+static int prefill_mma_launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                              const int* tiles, int num_tiles, const int* seg_q_start, const int* seg_pos0,
+                              const int* block_table, const int* table_rows, int table_stride, int H, int KV, int D, int ps,
+                              int tile_rows, float scale, int window, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     if ((D != 64 && D != 128) || H % KV || tile_rows != BQ || q_stride % 8) return -2;
     static bool configured[2] = {false, false};
@@ -223,15 +239,32 @@ MI_EXPORT int mi_attn_prefill_mma(const void* q, int q_stride, const void* k_cac
     const float scale_log2 = scale * 1.4426950408889634f;
 #define LAUNCH(DD, IDX) do { \
         if (!configured[IDX]) { \
-            cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<DD, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return (int)e; \
             configured[IDX] = true; \
         } \
-        attn_prefill_mma_kernel<DD><<<grid, PF_WARPS * 32, smem, stream>>>( \
+        attn_prefill_mma_kernel<DD, SPLIT><<<grid, PF_WARPS * 32, smem, stream>>>( \
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
             (__nv_bfloat16*)out, tiles, seg_q_start, seg_pos0, block_table, table_rows, table_stride, H, KV, ps, scale_log2, window); \
     } while (0)
     if (D == 128) LAUNCH(128, 0); else LAUNCH(64, 1);
 #undef LAUNCH
     return (int)cudaGetLastError();
+}
+
+MI_EXPORT int mi_attn_prefill_mma(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                  const int* tiles, int num_tiles, const int* seg_q_start, const int* seg_pos0,
+                                  const int* block_table, const int* table_rows, int table_stride, int H, int KV, int D, int ps,
+                                  int tile_rows, float scale, int window, cudaStream_t stream) {
+    return prefill_mma_launch<false>(q, q_stride, k_cache, v_cache, out, tiles, num_tiles, seg_q_start, seg_pos0, block_table, table_rows,
+                                     table_stride, H, KV, D, ps, tile_rows, scale, window, stream);
+}
+
+// The same with every softmax weight split into two bfloat16 numbers for the P V product (see SPLIT above).
+MI_EXPORT int mi_attn_prefill_mma_split(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                        const int* tiles, int num_tiles, const int* seg_q_start, const int* seg_pos0,
+                                        const int* block_table, const int* table_rows, int table_stride, int H, int KV, int D, int ps,
+                                        int tile_rows, float scale, int window, cudaStream_t stream) {
+    return prefill_mma_launch<true>(q, q_stride, k_cache, v_cache, out, tiles, num_tiles, seg_q_start, seg_pos0, block_table, table_rows,
+                                    table_stride, H, KV, D, ps, tile_rows, scale, window, stream);
 }

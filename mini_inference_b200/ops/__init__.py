@@ -521,8 +521,11 @@ class CudaOps:
         and dropped: 76-92 us against 59 us for the pair at 2,048 rows)."""
         return self.qk_norm_rope_cache(self.linear(h, w), H, KV, D, q_weight, k_weight, eps, inv_freq, meta, k_cache, v_cache)
 
-    def paged_attention(self, q, k_cache, v_cache, meta, H, KV, D, scale, window):
-        """meta: the step's arrays for this cache group.  seg_q_start, seg_pos0, seg_kv_len per entry; decode_segs (entries
+    def paged_attention(self, q, k_cache, v_cache, meta, H, KV, D, scale, window, split_weights=False):
+        """split_weights: the tensor-core kernels take every softmax weight into the P V product as TWO bfloat16 numbers (its
+        rounding and the rest: 16 mantissa bits, float32 sums) instead of one; the tcgen05 prompt kernel, which has no such
+        form, is left out.  The float32 kernels behind them compute the weights in float32 anyway.
+        meta: the step's arrays for this cache group.  seg_q_start, seg_pos0, seg_kv_len per entry; decode_segs (entries
         that feed one token), prefill_tiles / prefill_tiles2 ((entry, first row) per tile of meta.tile / 2 * meta.tile query
         rows); block_table [rows, max_pages] with entry i reading row table_rows[i] (row i when table_rows is None)."""
         T = q.shape[0]
@@ -536,7 +539,7 @@ class CudaOps:
         fast = (self.fast_attention and q.dtype == torch.bfloat16 and D in (64, 128) and q.stride(0) % 8 == 0
                 and q.data_ptr() % 16 == 0)
         tc = (fast and self.tc_attention and num_tiles and meta.tile == 64 and meta.page_size % 8 == 0
-              and 64 % meta.page_size == 0 and num_tiles2)
+              and 64 % meta.page_size == 0 and num_tiles2 and not split_weights)
         if tc:
             rc = self.lib.mi_attn_prefill_tc(
                 _p(q), q.stride(0), T, _p(k_cache), _p(v_cache), _c.c_longlong(k_cache.shape[0] * KV * meta.page_size),
@@ -546,7 +549,7 @@ class CudaOps:
             _check(rc, "attn_prefill_tc")
             self.launches += 1
         elif num_tiles and fast and meta.tile == 64:
-            _check(self.lib.mi_attn_prefill_mma(
+            _check((self.lib.mi_attn_prefill_mma_split if split_weights else self.lib.mi_attn_prefill_mma)(
                 _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), num_tiles,
                 _p(meta.seg_q_start), _p(meta.seg_pos0), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D,
                 meta.page_size, meta.tile, _c.c_float(scale), win, self._stream()), "attn_prefill_mma")
@@ -576,7 +579,7 @@ class CudaOps:
                 counters = self._merge_counters
             # without counters the splits stay in o_part / lse for the merge launch below: the cluster merge must be off too
             cluster = int(self.cluster_merge and counters is not None)
-            _check(self.lib.mi_attn_decode_mma_rows(
+            _check((self.lib.mi_attn_decode_mma_rows_split if split_weights else self.lib.mi_attn_decode_mma_rows)(
                 _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(o_part), _p(lse), _p(meta.decode_segs),
                 num_decode, _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), _p(rows), meta.max_pages,
                 H, KV, D, meta.page_size, S, _c.c_float(scale), win, _p(counters),
@@ -729,13 +732,22 @@ class CudaOps:
             # take it as it is (the pool given as keys AND values); the last R columns of each head's output are dropped
             o = self.paged_attention(q.view(T, H * (C + R)), cache, cache, meta, H, 1, C + R, scale, None)
             return o.view(T, H, C + R)[:, :, :C].permute(1, 0, 2)
-        out = torch.empty((H, T, C), dtype=q.dtype, device=q.device)
         num_decode, num_tiles = meta.decode_segs.shape[0], meta.prefill_tiles.shape[0]
-        code = _code(q.dtype)
+        code, Dk = _code(q.dtype), C + R
+        # Cached rows of 64 or 128 entries, bfloat16: the paged tensor-core kernels (mma.sync forms) with the pool as keys AND values
+        # of one shared kv head and every softmax weight split into two bfloat16 numbers for the P V product, which keeps the
+        # weights' precision where the design wants it; their output has C + R columns per head, of which the first C count.
+        if (q.dtype == torch.bfloat16 and Dk in (64, 128) and meta.tile == 64 and self.fast_attention and meta.page_size % 16 == 0
+                and q.data_ptr() % 16 == 0):
+            o = self.paged_attention(q.view(T, H * Dk), cache, cache, meta, H, 1, Dk, scale, None, split_weights=True)
+            return o.view(T, H, Dk)[:, :, :C].permute(1, 0, 2)
+        out = torch.empty((H, T, C), dtype=q.dtype, device=q.device)
+        buf, hs, ts = out, T * C, C
         if num_tiles:
-            _check(self.lib.mi_latent_prefill(_p(q), _p(cache), _p(out), _p(meta.prefill_tiles), num_tiles, _p(meta.seg_q_start),
-                                              _p(meta.seg_pos0), _p(meta.block_table), _p(meta.table_rows), meta.max_pages, T, H, C, R,
-                                              meta.page_size, meta.tile, _c.c_float(scale), code, self._stream()), "latent_prefill")
+            _check(self.lib.mi_latent_prefill(_p(q), _p(cache), _p(buf), _p(meta.prefill_tiles), num_tiles, _p(meta.seg_q_start),
+                                              _p(meta.seg_pos0), _p(meta.block_table), _p(meta.table_rows), meta.max_pages,
+                                              _c.c_longlong(hs), _c.c_longlong(ts), H, C, R, meta.page_size, meta.tile,
+                                              _c.c_float(scale), code, self._stream()), "latent_prefill")
             self.launches += 1
         if num_decode:
             S = self.choose_splits(num_decode * math.ceil(H / 4), meta.max_kv_len, 2)
@@ -743,10 +755,10 @@ class CudaOps:
             if S > 1:
                 o_part = torch.empty((num_decode, H, S, C), dtype=torch.float32, device=q.device)
                 lse = torch.empty((num_decode, H, S), dtype=torch.float32, device=q.device)
-            _check(self.lib.mi_latent_decode(_p(q), _p(cache), _p(out), _p(o_part), _p(lse), _p(meta.decode_segs), num_decode,
+            _check(self.lib.mi_latent_decode(_p(q), _p(cache), _p(buf), _p(o_part), _p(lse), _p(meta.decode_segs), num_decode,
                                              _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), _p(meta.table_rows),
-                                             meta.max_pages, T, H, C, R, meta.page_size, S, _c.c_float(scale), code, self._stream()),
-                   "latent_decode")
+                                             meta.max_pages, _c.c_longlong(hs), _c.c_longlong(ts), H, C, R, meta.page_size, S,
+                                             _c.c_float(scale), code, self._stream()), "latent_decode")
             self.launches += 2 if S > 1 else 1
         return out
 

@@ -230,6 +230,8 @@ SINGLE = {
     "channel_delta_taps4": config(36, 67, [delta(2, 2, 20, 33, 4)]),
     "latent": config(40, 71, [latent(3, 8, 6, 10, 12)]),
     "latent_part_rotated": config(40, 71, [latent(2, 4, 12, 6, 20, dims=8, base=100.0)]),
+    # cached rows of 64 entries: in bfloat16 on the GPU prompt portions take the tensor-core kernel with split softmax weights
+    "latent_rows64": config(40, 71, [latent(3, 8, 16, 10, 48)]),
     # sizes that put every view of a fused product on an odd offset and every row on an odd length
     "lightning_odd": config(27, 53, [light(3, 5, 7, [0.4, 0.8, 0.95])]),
     "channel_delta_odd": config(27, 53, [delta(3, 1, 9, 6, 3, rank=3)]),
@@ -519,13 +521,47 @@ def test_kernels_against_the_stand_ins():
 @pytest.mark.parametrize("L,far", [(300, 0), (300, 7), (257, 255), (256, 16), (129, 128), (64, 15), (5, 4), (1500, 31), (1500, 1023)])
 def test_a_far_key_among_hundreds_on_gpu(L, far, dtype):
     ops = cuda_ops()
-    for splits in (None, 3):
-        ops.force_splits = splits
+    for C, R in ((24, 8), (48, 16), (96, 32)):           # rows of 64 and 128 entries reach the tensor-core decode kernel in bfloat16
+        for splits in (None, 3):
+            ops.force_splits = splits
+            try:
+                out, want = far_key_case(ops, "cuda:0", dtype, L, far, page=16, C=C, R=R)
+            finally:
+                ops.force_splits = None
+            assert (out - want).abs().max() < (1e-3 if dtype == torch.float32 else 2e-2) * want.abs().max() + 1e-6
+
+
+@gpu
+def test_split_weight_prompt_attention_against_the_float32_kernel():
+    """Latent rows of 64 and 128 entries, bfloat16: prompt portions (on the mma kernel with every softmax weight as two bfloat16
+    numbers) beside decoded tokens (float32 kernel) in one step, against the float32 kernels alone on the same inputs."""
+    from types import SimpleNamespace
+    ops = cuda_ops()
+    g = torch.Generator().manual_seed(5)
+    for C, R, H in ((48, 16, 3), (96, 32, 5)):
+        lens, pos0 = [70, 1, 130, 1], [10, 199, 0, 64]
+        page, pages_per = 16, 14
+        T = sum(lens)
+        cache = (torch.randn(4 * pages_per + 1, 1, page, C + R, generator=g) * 0.5).to("cuda:0", torch.bfloat16)
+        table = torch.zeros(5, pages_per, dtype=torch.int32)
+        for i in range(4):
+            table[i + 1] = torch.randperm(pages_per, generator=g).to(torch.int32) + 1 + i * pages_per
+        qs = [0, 70, 71, 201, 202]
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda:0")      # noqa: E731
+        tiles = [(i, r) for i, n in enumerate(lens) if n > 1 for r in range(0, n, 64)]
+        meta = SimpleNamespace(seg_q_start=i32(qs), seg_pos0=i32(pos0), seg_kv_len=i32([p + n for p, n in zip(pos0, lens)]), table_rows=i32([1, 2, 3, 4]),
+                               block_table=table.to("cuda:0"), max_pages=pages_per, page_size=page, decode_segs=i32([1, 3]),
+                               prefill_tiles=i32(tiles).view(-1, 2), tile=64, max_kv_len=200)
+        q = torch.randn(T, H, C + R, generator=g).to("cuda:0", torch.bfloat16)
+        got = ops.latent_attention(q, cache, meta, H, C, R, 0.2).float()
+        ops.fast_attention = False
         try:
-            out, want = far_key_case(ops, "cuda:0", dtype, L, far, page=16)
+            want = ops.latent_attention(q, cache, meta, H, C, R, 0.2).float()
         finally:
-            ops.force_splits = None
-        assert (out - want).abs().max() < (1e-3 if dtype == torch.float32 else 2e-2) * want.abs().max() + 1e-6
+            ops.fast_attention = True
+        assert got.shape == want.shape == (H, T, C)
+        assert (got - want).abs().max() <= 2e-2 * want.abs().max()
+    ops.check_errors()
 
 
 @gpu
