@@ -39,7 +39,7 @@ def dense_ff(h, w, pre, eps):
 
 
 def causal_conv(x, taps_w):
-    """x [T, C], taps_w [C, taps]; the last column multiplies the current token; zeros before the start."""
+    """x [T, C], taps_w [C, taps]: out[t] = sum_j taps_w[:, j] * x[t - (taps - 1 - j)], terms with a negative index left out."""
     T, C = x.shape
     taps = taps_w.shape[1]
     out = torch.zeros_like(x)
