@@ -7,7 +7,6 @@ Notation: h is a mixer's input [T, width]; weights are [out, in]; positions coun
 from __future__ import annotations
 
 import json
-import math
 import os
 import struct
 
@@ -23,10 +22,6 @@ def rms(x, eps):
 
 def scalar_norm(x, g, eps):
     return rms(x, eps) * g
-
-
-def gelu_tanh(z):
-    return 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
 
 
 def polynorm(z, coef, eps):
