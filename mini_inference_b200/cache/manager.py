@@ -51,6 +51,7 @@ class _Group:
         self.need, self.steps = need, steps
         self.pool: Optional[PagePool] = None
         self.storage = None                              # kv groups
+        self.value_storage = None                        # kv groups whose value rows have a size of their own
         self.tables: Optional[np.ndarray] = None         # [slots + 1, max_pages] int32 (host)
         self.device_table = None                         # the same on the device, kept current by update lists
         self.dirty: dict = {}                            # flat index -> None, in the order the entries changed
@@ -91,11 +92,20 @@ class CacheManager:
             if allocate:
                 g.device_table = torch.zeros((max_seqs + 1, self.max_pages_per_seq), dtype=torch.int32, device=self.device)
                 n = g.need
-                g.storage = torch.zeros((len(g.steps), n.planes, num_pages + 1, n.num_kv_heads, page_size, n.head_dim),
-                                        dtype=dtype, device=self.device)
+                g.value_storage = None
+                if n.planes == 2 and n.value_dim not in (None, n.head_dim):      # value rows of another size: a pool of their own
+                    g.storage = torch.zeros((len(g.steps), 1, num_pages + 1, n.num_kv_heads, page_size, n.head_dim),
+                                            dtype=dtype, device=self.device)
+                    g.value_storage = torch.zeros((len(g.steps), num_pages + 1, n.num_kv_heads, page_size, n.value_dim),
+                                                  dtype=dtype, device=self.device)
+                else:
+                    g.storage = torch.zeros((len(g.steps), n.planes, num_pages + 1, n.num_kv_heads, page_size, n.head_dim),
+                                            dtype=dtype, device=self.device)
             for j, step in enumerate(g.steps):
                 k = g.storage[j, 0] if allocate else None
-                v = g.storage[j, 1] if allocate and g.need.planes > 1 else None
+                v = g.storage[j, 1] if allocate and g.need.planes > 1 and g.value_storage is None else None
+                if allocate and g.value_storage is not None:
+                    v = g.value_storage[j]
                 self.layer_caches[step] = LayerCache(gi, k=k, v=v)
         for g in self.state_groups:
             if allocate:
@@ -111,7 +121,9 @@ class CacheManager:
     def bytes_per_token(self) -> int:
         """Bytes of cache one token occupies over all groups (engine/core/kv_cache.py:22-30)."""
         el = torch.empty((), dtype=self.dtype).element_size()
-        return sum(g.need.planes * len(g.steps) * g.need.num_kv_heads * g.need.head_dim * el for g in self.kv_groups)
+        def row(n):
+            return n.head_dim + n.value_dim if n.planes == 2 and n.value_dim is not None else n.planes * n.head_dim
+        return sum(row(g.need) * len(g.steps) * g.need.num_kv_heads * el for g in self.kv_groups)
 
     def state_bytes_per_seq(self) -> int:
         """Bytes of fixed-size state one live request occupies over all state groups."""

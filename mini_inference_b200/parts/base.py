@@ -80,11 +80,13 @@ class WeightSpec:
 class KVCacheNeed:
     """Keys and values in pages; window=None keeps every key, W keeps the last W.  planes: 2 = a key and a value
     pool; 1 = one pool of rows per token (a mixer that caches one compressed vector per token and derives both
-    keys and values from it); the LayerCache then has no v."""
+    keys and values from it); the LayerCache then has no v.  value_dim: the size of a value row when it differs from a
+    key row's (head_dim); the value pool is then a tensor of its own."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     planes: int = 2
+    value_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -108,6 +110,19 @@ class StepContext:
         self.ops, self.batch, self.dtype, self.device = ops, batch, dtype, device
         self.defer_ok = False        # set by the model when every reader of a block's outputs accepts deferred sums
         self.hints_ok = False        # the kernel namespace's add_rmsnorm takes next_weight=
+        self.shared = {}             # what a part leaves for later parts of the SAME step, by a key the parts agree on
+        self._rows = (None, None)    # (stream, its rows in the run's dtype): see note_rows
+
+    def note_rows(self, stream, rows):
+        """A kernel that wrote the float32 stream also wrote its rows in the run's dtype: whoever reads the stream next
+        (a block whose sublayers read the stream itself) takes them instead of converting again."""
+        self._rows = (stream, rows)
+
+    def rows_of(self, stream):
+        """The stream's rows in the run's dtype."""
+        if self._rows[0] is stream:
+            return self._rows[1]
+        return stream if stream.dtype == self.dtype else self.ops.cast_rows(stream, self.dtype)
 
 
 class Part:

@@ -58,3 +58,33 @@ class PreNormBlock(Part):
 class PreNormMixerOnly(PreNormBlock):
     """A layer without feed-forward: x = x + mixer(norm1(x))."""
     roles = {"mixer": "mixer", "norm1": "norm", "position": "position"}
+
+
+@register_block("outnorm")
+class OutputNormBlock(Part):
+    """Sublayers read the stream itself and their OUTPUT is normed before it joins the stream:
+    x <- x + norm1(mixer(x)); x <- x + norm2(feed_forward(x)), the norms being of the kind that offers add_normed
+    (they own the multiplier and the layer scale).  The stream is float32; the sublayers get its rows in the run's
+    dtype, which the norm kernel that last wrote the stream has left in the step context."""
+    roles = {"mixer": "mixer", "feed_forward": "feed_forward", "norm1": "norm", "norm2": "norm", "position": "position"}
+
+    def __init__(self, spec, parts):
+        super().__init__(spec)
+        self.parts = dict(parts)
+        self.mixer, self.feed_forward = parts["mixer"], parts.get("feed_forward")
+        self.norm1, self.norm2, self.position = parts["norm1"], parts.get("norm2"), parts["position"]
+
+    def forward(self, x, delta, ctx, cache, owns_cache=True, pre_add=None):
+        if delta is not None or pre_add is not None:
+            raise ValueError("the output-norm arrangement carries no pending addition and takes no pass vector")
+        h = ctx.rows_of(x)
+        h = self.norm1.add_normed(x, self.mixer.forward(h, ctx, cache, self.position, owns_cache), ctx)
+        if self.feed_forward is not None:
+            self.norm2.add_normed(x, self.feed_forward.forward(h, ctx), ctx)
+        return x, None
+
+
+@register_block("outnorm_mixer")
+class OutputNormMixerOnly(OutputNormBlock):
+    """A layer without feed-forward: x <- x + norm1(mixer(x))."""
+    roles = {"mixer": "mixer", "norm1": "norm", "position": "position"}

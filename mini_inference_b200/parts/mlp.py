@@ -81,3 +81,59 @@ class PolyNormMLP(Part):
     def forward(self, h, ctx):
         ops = ctx.ops
         return ops.linear(ops.polynorm(ops.linear(h, self.up), self.coef, self.eps), self.down)
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(Part):
+    """A mixture of small gated feed-forwards of which each token uses `top`, plus an optional expert that every token uses.
+
+    Router (float32): s = softmax(W_r h) over all experts; the CHOICE is made on s + correction, confined to the `keep`
+    groups (of `count` equal groups of neighbouring experts) whose best choice score is largest; the chosen experts'
+    weights are their plain s, not renormalised.  Expert: g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit),
+    y = g * sigmoid(gate_slope * g) * (u + 1), output W_down y.  The token's output is the weighted sum over its experts
+    (added in the order of choice, in float32) plus the shared expert's output."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        g = spec.get
+        self.hidden, self.E, self.top, self.F = int(g("hidden_size")), int(g("num_experts")), int(g("top")), int(g("expert_size"))
+        self.groups = tuple(g("groups")) if g("groups") else None
+        self.limit, self.slope = float(g("limit")), float(g("gate_slope", 1.702))
+        self.shared_size = g("shared_size")
+        self.shared_limit = float(g("shared_limit")) if self.shared_size else None
+        self.router = self.correction = self.w_in = self.w_out = self.shared_in = self.shared_out = None
+
+    def weight_specs(self):
+        hid, F = self.hidden, self.F
+        specs = [WeightSpec("router", (self.E, hid)), WeightSpec("correction", (self.E,), kind="vector", init="zeros")]
+        for e in range(self.E):
+            specs += [WeightSpec(f"e{e}.gate", (F, hid)), WeightSpec(f"e{e}.up", (F, hid)), WeightSpec(f"e{e}.down", (hid, F))]
+        if self.shared_size:
+            S = int(self.shared_size)
+            specs += [WeightSpec("shared.gate", (S, hid)), WeightSpec("shared.up", (S, hid)), WeightSpec("shared.down", (hid, S))]
+        return specs
+
+    def load(self, tensors, dtype, device):
+        self.router = tensors.pop("router").float().contiguous()           # the router's logits are float32 sums
+        self.correction = tensors.pop("correction").float().contiguous()
+        # per expert [gate rows | up rows] and the down matrix, stacked: one grouped product each
+        self.w_in = torch.stack([torch.cat([tensors.pop(f"e{e}.gate"), tensors.pop(f"e{e}.up")], dim=0) for e in range(self.E)]).contiguous()
+        self.w_out = torch.stack([tensors.pop(f"e{e}.down") for e in range(self.E)]).contiguous()
+        if self.shared_size:
+            self.shared_in = torch.cat([tensors.pop("shared.gate"), tensors.pop("shared.up")], dim=0).contiguous()
+            self.shared_out = tensors.pop("shared.down")
+
+    @property
+    def first_weight(self):
+        return self.shared_in if self.shared_size else None
+
+    def step_flops(self, rows, pairs):
+        return 2 * rows * self.top * 3 * self.F * self.hidden      # the chosen experts' three products (the stacked tensors are not matrices)
+
+    def forward(self, h, ctx):
+        ops = ctx.ops
+        chosen, weights = ops.route_topk(h, self.router, self.correction, self.top, self.groups)
+        shared = None
+        if self.shared_size:
+            shared = ops.linear(ops.clamped_glu(ops.linear(h, self.shared_in), self.shared_limit, self.slope), self.shared_out)
+        return ops.expert_ffn(h, chosen, weights, self.w_in, self.w_out, self.limit, self.slope, shared)

@@ -176,6 +176,9 @@ class DecoderModel:
         ctx.hints_ok = getattr(ops, "takes_hints", False)
         if self.embedding_norm is not None:                    # gather and norm in one kernel; the stream starts normed
             x = self.embedding_norm.embed(b.token_ids, self.embedding, ctx, float32=self.spec.residual == "float32")
+        elif self.spec.residual == "float32":                  # the stream in float32 and, beside it, its rows in the run's dtype
+            x, rows = ops.embed_stream(b.token_ids, self.embedding, ctx.dtype)
+            ctx.note_rows(x, rows)
         else:
             x = ops.embedding(b.token_ids, self.embedding)
         for position in self._positions.values():

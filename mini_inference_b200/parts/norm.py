@@ -54,3 +54,59 @@ class ScalarRMSNorm(Part):
 
     def forward(self, x, delta, ctx, rows=None, pre_add=None):
         return ctx.ops.add_scaled_rmsnorm(x, delta, self.weight, self.eps, rows, pre_add, ctx.dtype)
+
+
+@register_norm("stream_rmsnorm")
+class StreamRMSNorm(Part):
+    """y = w * x / sqrt(mean(x^2) + eps) on a float32 residual stream, rows handed out in the run's dtype
+    (a pending delta, if any, is added to the stream first, in float32)."""
+    keeps_float32_stream = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.size, self.eps = int(spec.get("size")), float(spec.get("eps"))
+        self.weight = None
+
+    def weight_specs(self):
+        return [WeightSpec("weight", (self.size,), kind="vector", init="norm")]
+
+    def load(self, tensors, dtype, device):
+        self.weight = tensors["weight"].float().contiguous()
+
+    def forward(self, x, delta, ctx, rows=None, pre_add=None):
+        if pre_add is not None:
+            raise ValueError("stream_rmsnorm takes no pass vector")
+        return ctx.ops.stream_rmsnorm(x, delta, self.weight, self.eps, rows, ctx.dtype)
+
+
+@register_norm("out_rmsnorm")
+class OutputRMSNorm(Part):
+    """The norm of an arrangement that norms what a sublayer RETURNS: x <- x + mult * scale * (w * y / rms(y)), with w the
+    norm's weight, scale a layer-scale vector (layer_scale=False: none) and mult one number.  x is the float32 stream;
+    one kernel norms y, adds to x in float32 and writes x's rows in the run's dtype for the next reader of the stream."""
+    keeps_float32_stream = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.size, self.eps, self.mult = int(spec.get("size")), float(spec.get("eps")), float(spec.get("mult", 1.0))
+        self.layer_scale = bool(spec.get("layer_scale", False))
+        self.weight = self.scale = None
+
+    def weight_specs(self):
+        specs = [WeightSpec("weight", (self.size,), kind="vector", init="norm")]
+        if self.layer_scale:
+            specs.append(WeightSpec("scale", (self.size,), kind="vector", init="norm"))
+        return specs
+
+    def load(self, tensors, dtype, device):
+        self.weight = tensors["weight"].float().contiguous()
+        self.scale = tensors["scale"].float().contiguous() if self.layer_scale else None
+
+    def add_normed(self, x, y, ctx):
+        """Adds the normed y to the stream x (in place) and returns x's rows in the run's dtype."""
+        rows = ctx.ops.out_rmsnorm_add(x, y, self.weight, self.scale, self.mult, self.eps, ctx.dtype)
+        ctx.note_rows(x, rows)
+        return rows
+
+    def forward(self, x, delta, ctx, rows=None, pre_add=None):
+        raise TypeError("out_rmsnorm norms a sublayer's output (add_normed); it is not a norm of the stream")

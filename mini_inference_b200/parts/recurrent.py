@@ -146,3 +146,47 @@ class ChannelDeltaRule(Part):
         o = ops.delta_scan(prep, H, KV, D, V, cache.state, ctx.batch)                   # float32 [T, H V]
         rows = ops.group_rmsnorm_gate(o, self.norm, gate, self.eps, H, V, ctx.dtype)
         return rows, self.o
+
+
+@register_mixer("retention")
+class Retention(Part):
+    """q, k = rotate(W h) (the position part's rotate-half frequencies on the first coordinates of each head; none: no
+    rotation), k also * key_dim^-1/2 after the rotation;  S <- decay_h S + k v^T;  o = S^T q;
+    rows: per head o / rms(o) (no weight), * silu(W_g h).  What enters the recurrence is float32."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        g = spec.get
+        self.hidden, self.H, self.D, self.V = int(g("hidden_size")), int(g("num_heads")), int(g("key_dim")), int(g("value_dim"))
+        self.decay_values = tuple(float(v) for v in g("decay"))
+        self.eps = float(g("out_norm_eps"))
+        if len(self.decay_values) != self.H:
+            raise ValueError(f"{len(self.decay_values)} decay constants for {self.H} heads")
+        self.proj = self.o = self.decay = None
+
+    def weight_specs(self):
+        H, D, V, hid = self.H, self.D, self.V, self.hidden
+        return [WeightSpec("q", (H * D, hid)), WeightSpec("k", (H * D, hid)), WeightSpec("v", (H * V, hid)),
+                WeightSpec("g", (H * V, hid)), WeightSpec("o", (hid, H * V))]
+
+    def cache_need(self):
+        return StateNeed((self.H * self.D * self.V,), "float32")
+
+    def load(self, tensors, dtype, device):
+        self.proj = torch.cat([tensors.pop(n) for n in ("q", "k", "v", "g")], dim=0).contiguous()     # one product for all four
+        self.o = tensors.pop("o")
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=device)
+
+    @property
+    def first_weight(self):
+        return self.proj
+
+    def step_flops(self, rows, pairs):
+        return 4 * self.H * self.D * self.V * rows
+
+    def forward(self, h, ctx, cache, position, owns_cache=True):
+        ops, H, D, V = ctx.ops, self.H, self.D, self.V
+        p = ops.linear(h, self.proj)                                # [T, 2 H D + 2 H V]: q | k | v | gate
+        o = ops.retention_scan(p, H, D, V, position.rotary_inv_freq(), float(D) ** -0.5, self.decay, cache.state, ctx.batch)
+        rows = ops.group_rmsnorm_gate(o, None, p[:, 2 * H * D + H * V:], self.eps, H, V, ctx.dtype, act="silu")
+        return ops.linear(rows, self.o)

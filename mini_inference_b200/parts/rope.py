@@ -61,3 +61,27 @@ class InterleavedRotary(Part):
 
     def on_embedding(self, x, ctx):
         return x
+
+
+@register_position("rotary_half")
+class HalfRotary(Part):
+    """Rotary encoding of the first `dims` coordinates of a vector in the rotate-half layout: coordinate i is paired with
+    i + dims/2, and the pair (u, v) at position p becomes (u cos a - v sin a, v cos a + u sin a), a = p * theta^(-2i/dims);
+    coordinates from `dims` on pass unchanged.  The frequencies are made on the host in float64 and rounded once to
+    float32; angle, cos and sin are float32 inside the kernel."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.dims = int(spec.get("dims"))
+        self.theta = float(spec.get("theta"))
+        self._inv_freq = None
+
+    def load(self, tensors, dtype, device):
+        i = torch.arange(0, self.dims // 2, dtype=torch.float64)
+        self._inv_freq = (self.theta ** (-2.0 * i / self.dims)).to(torch.float32).to(device)
+
+    def rotary_inv_freq(self):
+        return self._inv_freq
+
+    def on_embedding(self, x, ctx):
+        return x

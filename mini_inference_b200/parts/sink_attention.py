@@ -1,0 +1,84 @@
+"""Softmax attention over the paged cache whose mask, softmax and inputs are chosen by constants:
+
+  unit norm    q and k are divided by their root mean square per head (no weight) instead of being rotated;
+               positions do not enter the scores
+  block_size   B: position i sees j <= i only inside its own block of B positions, floor(i / B) = floor(j / B),
+               blocks counted from position 0 of the sequence (None: every j <= i); window: the last W keys (None: all)
+  sink         the softmax has one more term whose score is 0 and which carries no value:
+               p_j = exp(s_j) / (1 + sum_j exp(s_j))
+  value_mix    "source": this layer's values are left in the step context for later layers;
+               "blend": v <- (1 - lambda) v + lambda v_source with lambda the tensor `vmix` and v_source the source
+               layer's values of the same tokens; the blended v is what is cached
+  key and value rows may differ in size (key_dim, value_dim); the value pool is then a tensor of its own.
+
+q, k, v come from one product; one kernel norms q and k, blends v and writes k and v into the step's pages
+before attention runs, so a portion attends to itself through the cache.  Scores, softmax weights and the weighted
+sum are float32."""
+from __future__ import annotations
+
+import torch
+
+from .attention import paged_attention_step_arrays
+from .base import KVCacheNeed, Part, WeightSpec, register_mixer
+
+
+@register_mixer("sink_attention")
+class SinkAttention(Part):
+    step_arrays_key = "paged_attention"
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        g = spec.get
+        self.hidden, self.H, self.KV = int(g("hidden_size")), int(g("num_heads")), int(g("num_kv_heads"))
+        self.D, self.V, self.scale = int(g("key_dim")), int(g("value_dim")), float(g("scale"))
+        self.eps = g("unit_norm_eps")                       # None: q and k are used as projected
+        self.block_size, self.window, self.sink = g("block_size"), g("window"), bool(g("sink", False))
+        self.value_mix = g("value_mix")
+        self.mix_key = g("value_mix_key", "values")
+        if self.H % self.KV:
+            raise ValueError(f"{self.H} query heads are not a multiple of {self.KV} kv heads")
+        if self.value_mix not in (None, "source", "blend"):
+            raise ValueError(f"value_mix '{self.value_mix}' is not one of source, blend")
+        self.qkv = self.o = self.lam = None
+
+    def weight_specs(self):
+        H, KV, D, V, hid = self.H, self.KV, self.D, self.V, self.hidden
+        specs = [WeightSpec("q", (H * D, hid)), WeightSpec("k", (KV * D, hid)), WeightSpec("v", (KV * V, hid)),
+                 WeightSpec("o", (hid, H * V))]
+        if self.value_mix:                                  # a source layer's checkpoint holds the number too; it is not used
+            specs.append(WeightSpec("vmix", (), kind="vector", init="norm"))
+        return specs
+
+    def cache_need(self):
+        return KVCacheNeed(self.KV, self.D, self.window, value_dim=None if self.V == self.D else self.V)
+
+    def load(self, tensors, dtype, device):
+        self.qkv = torch.cat([tensors.pop("q"), tensors.pop("k"), tensors.pop("v")], dim=0).contiguous()
+        self.o = tensors.pop("o")
+        if self.value_mix == "blend":
+            self.lam = tensors["vmix"].float().reshape(1).contiguous()
+
+    step_arrays = staticmethod(paged_attention_step_arrays)
+
+    @property
+    def first_weight(self):
+        return self.qkv
+
+    def step_flops(self, rows, pairs):
+        return 2 * self.H * (self.D + self.V) * pairs
+
+    def forward(self, h, ctx, cache, position, owns_cache=True):
+        ops, H, KV, D, V = ctx.ops, self.H, self.KV, self.D, self.V
+        meta = ctx.batch.group_view(cache.group, self.step_arrays_key)
+        p = ops.linear(h, self.qkv)                                        # [T, H D + KV D + KV V]
+        source = None
+        if self.value_mix == "blend":
+            source = ctx.shared.get(("value_mix", self.mix_key))
+            if source is None or source.shape[1] != KV * V:
+                raise ValueError("a layer that blends values in runs before the layer that lends them, or their sizes differ")
+        elif self.value_mix == "source":
+            ctx.shared[("value_mix", self.mix_key)] = p[:, (H + KV) * D:]      # a view: the kernel below leaves these columns alone
+        q = ops.unit_qk_cache(p, H, KV, D, V, self.eps, self.lam, source, meta,
+                              cache.k if owns_cache else None, cache.v if owns_cache else None)
+        o = ops.masked_attention(q, cache.k, cache.v, meta, H, KV, D, V, self.scale, self.block_size, self.window, self.sink)
+        return ops.linear(o, self.o)

@@ -164,11 +164,13 @@ def _lightning_scan(self, p, H, D, V, decay, state, batch):
     return o
 
 
-def _group_rmsnorm_gate(self, o, weight, gate, eps, groups, gs, out_dtype):
+def _group_rmsnorm_gate(self, o, weight, gate, eps, groups, gs, out_dtype, act="sigmoid"):
     T = o.shape[0]
     y = _rms(o.view(T, groups, gs), eps).reshape(T, groups * gs)
-    y = y * weight.float().repeat(groups * gs // weight.numel())
-    return (y * torch.sigmoid(gate.float())).to(out_dtype)
+    if weight is not None:
+        y = y * weight.float().repeat(groups * gs // weight.numel())
+    g = gate.float()
+    return (y * (torch.sigmoid(g) if act == "sigmoid" else g * torch.sigmoid(g))).to(out_dtype)
 
 
 def _delta_prepare(self, p, a, conv, A_log, dt_bias, H, KV, D, V, taps, unit_eps, state, batch):
@@ -269,7 +271,143 @@ def _head_gate(self, o, gate, out_dtype):
     return (o.float() * torch.sigmoid(gate.float()).T[:, :, None]).transpose(0, 1).reshape(T, H * V).to(out_dtype)
 
 
+# ---------------------------------------------------------------- output norms, block-local sink attention, retention, routed experts
+def _embed_stream(self, ids, table, rows_dtype):
+    x = table[ids.long()].float()
+    return x, (x if rows_dtype == torch.float32 else x.to(rows_dtype))
+
+
+def _cast_rows(self, x, dtype):
+    return x.to(dtype)
+
+
+def _out_rmsnorm_add(self, x, y, weight, scale, mult, eps, rows_dtype):
+    n = _rms(y.float(), eps) * weight.float()
+    if scale is not None:
+        n = n * scale.float()
+    x.add_(mult * n)
+    return x if rows_dtype == torch.float32 else x.to(rows_dtype)
+
+
+def _stream_rmsnorm(self, x, delta, weight, eps, rows, out_dtype):
+    if rows is None:
+        if delta is not None:
+            x.add_(delta.float())
+        src = x
+    else:
+        src = x[rows.long()]
+        if delta is not None:
+            src = src + delta[rows.long()].float()
+    return (_rms(src, eps) * weight.float()).to(out_dtype)
+
+
+def _unit_qk_cache(self, p, H, KV, D, V, eps, lam, source, meta, k_cache, v_cache):
+    T, dt = p.shape[0], p.dtype
+    q = p[:, :H * D].float().view(T, H, D)
+    k = p[:, H * D:(H + KV) * D].float().view(T, KV, D)
+    v = p[:, (H + KV) * D:].float().view(T, KV, V)
+    if eps is not None:
+        q, k = _rms(q, eps), _rms(k, eps)
+    if source is not None:
+        v = (1.0 - lam.float()) * v + lam.float() * source.float().view(T, KV, V)
+    p[:, :H * D] = q.reshape(T, H * D).to(dt)
+    if k_cache is not None:
+        page, off = meta.slots.long() // meta.page_size, meta.slots.long() % meta.page_size
+        k_cache[page, :, off, :] = k.to(dt)
+        v_cache[page, :, off, :] = v.to(dt)
+    return p[:, :H * D]
+
+
+def _masked_attention(self, q, k_cache, v_cache, meta, H, KV, D, V, scale, block_size, window, sink):
+    T = q.shape[0]
+    out = torch.empty((T, H * V), dtype=q.dtype, device=q.device)
+    q_start, pos0, kv_len = meta.seg_q_start.tolist(), meta.seg_pos0.tolist(), meta.seg_kv_len.tolist()
+    ps = meta.page_size
+    rows = getattr(meta, "table_rows", None)
+    rows = list(range(len(pos0))) if rows is None else rows.tolist()
+    for s in range(len(pos0)):
+        a, b, L = q_start[s], q_start[s + 1], kv_len[s]
+        j = torch.arange(L, device=q.device)
+        pages = meta.block_table[rows[s], j // ps].long()
+        k = k_cache[pages, :, j % ps, :].float().repeat_interleave(H // KV, dim=1)        # [L, H, D]
+        v = v_cache[pages, :, j % ps, :].float().repeat_interleave(H // KV, dim=1)        # [L, H, V]
+        p = pos0[s] + torch.arange(b - a, device=q.device)
+        visible = j[None, :] <= p[:, None]
+        if window is not None:
+            visible &= j[None, :] > p[:, None] - window
+        if block_size is not None:
+            visible &= (j[None, :] // block_size) == (p[:, None] // block_size)
+        sc = torch.einsum("phd,jhd->hpj", q[a:b].reshape(b - a, H, D).float(), k) * scale
+        sc = sc.masked_fill(~visible[None], float("-inf"))
+        m = sc.max(-1, keepdim=True).values
+        if sink:
+            m = m.clamp_min(0.0)
+        e = torch.exp(sc - m)
+        den = e.sum(-1, keepdim=True) + (torch.exp(-m) if sink else 0.0)
+        out[a:b] = torch.einsum("hpj,jhd->phd", e / den, v).reshape(b - a, H * V).to(q.dtype)
+    return out
+
+
+def _retention_scan(self, p, H, D, V, inv_freq, k_scale, decay, state, batch):
+    T = p.shape[0]
+    q = p[:, :H * D].float().view(T, H, D).clone()
+    k = p[:, H * D:2 * H * D].float().view(T, H, D).clone()
+    v = p[:, 2 * H * D:2 * H * D + H * V].float().view(T, H, V)
+    if inv_freq is not None:
+        half = inv_freq.numel()
+        ang = batch.positions.float()[:, None] * inv_freq.float()[None, :]
+        cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        for t in (q, k):
+            a, b = t[..., :half].clone(), t[..., half:2 * half].clone()
+            t[..., :half] = a * cos - b * sin
+            t[..., half:2 * half] = b * cos + a * sin
+    k = k * k_scale
+    o = torch.zeros(T, H * V, dtype=torch.float32, device=p.device)
+    for a, b, slot in _segments(batch):
+        S = state[slot].view(H, D, V).clone()
+        for t in range(a, b):
+            S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
+            o[t] = torch.einsum("hdv,hd->hv", S, q[t]).reshape(-1)
+        state[slot] = S.reshape(-1)
+    return o
+
+
+def _route_topk(self, h, router, correction, top, groups):
+    s = torch.softmax(h.float() @ router.float().T, dim=-1)
+    choice = s + correction.float()
+    if groups:
+        count, keep = groups
+        best = choice.view(choice.shape[0], count, -1).max(-1).values
+        kept = torch.zeros_like(best, dtype=torch.bool).scatter_(1, best.topk(keep, dim=-1).indices, True)
+        choice = choice.masked_fill(~kept.repeat_interleave(choice.shape[1] // count, dim=1), float("-inf"))
+    idx = choice.topk(top, dim=-1).indices
+    return idx.to(torch.int32), s.gather(1, idx)
+
+
+def _clamped_glu(self, gu, limit, slope):
+    g, u = gu.float().chunk(2, dim=-1)
+    g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+    return (g * torch.sigmoid(slope * g) * (u + 1.0)).to(gu.dtype)
+
+
+def _expert_ffn(self, h, chosen, weights, w_in, w_out, limit, slope, shared):
+    T, top = chosen.shape
+    acc = torch.zeros(T, w_out.shape[1], dtype=torch.float32, device=h.device)
+    for j in range(top):                                   # in the order of choice
+        y = torch.empty(T, w_out.shape[1], dtype=h.dtype, device=h.device)
+        for e in chosen[:, j].unique().tolist():
+            rows = (chosen[:, j] == e).nonzero().flatten()
+            a = _clamped_glu(self, self.linear(h[rows], w_in[e]), limit, slope)
+            y[rows] = self.linear(a, w_out[e])
+        acc += weights[:, j:j + 1].float() * y.float()
+    if shared is not None:
+        acc += shared.float()
+    return acc.to(h.dtype)
+
+
 for _name, _fn in list(globals().items()):
     if _name.startswith("_") and _name[1:] in ("embed_scaled_norm", "add_scaled_rmsnorm", "polynorm", "lightning_scan", "group_rmsnorm_gate",
-                                               "delta_prepare", "delta_scan", "batched_linear", "latent_prepare", "latent_attention", "head_gate"):
+                                               "delta_prepare", "delta_scan", "batched_linear", "latent_prepare", "latent_attention", "head_gate",
+                                               "embed_stream", "cast_rows", "out_rmsnorm_add", "stream_rmsnorm", "unit_qk_cache", "masked_attention",
+                                               "retention_scan", "route_topk", "clamped_glu", "expert_ffn"):
         setattr(TorchRefOps, _name[1:], _fn)
