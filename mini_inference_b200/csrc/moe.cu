@@ -1,0 +1,266 @@
+// Routed feed-forward: a float32 router with group-limited top-k choice, a device-side sort of the (token, choice)
+// pairs by expert, two grouped products over the sorted rows, and the weighted sum per token.
+//
+//   route_topk   one block per token: logits = W_r h as float32 sums in a fixed order, s = softmax over all experts,
+//                choice scores c = s + correction; with groups, only experts of the `keep` groups (equal groups of
+//                neighbouring experts) whose largest c is largest stay eligible (the others count as -inf); the `top`
+//                largest c are chosen (ties: the lower index); the weights are the chosen experts' s, as they are.
+//   align        pairs p = token * top + j counted per expert; every expert's rows start on a multiple of the row tile
+//                (padding rows are marked -1), so a tile of rows belongs to ONE expert: tile_expert[tile] (-1 past the end).
+//                Nothing returns to the host: the grids of the products cover the most tiles there can be, and a block
+//                whose tile has no expert leaves at once.
+//   grouped in   rows gathered by token; per expert [gate rows | up rows]; the epilogue applies
+//                g = min(gate, limit), u = clamp(up, -limit, limit), y = g * sigmoid(slope * g) * (u + 1).
+//   grouped out  y rows times the expert's down matrix, written to the pair's own row (so the order of pairs inside an
+//                expert's segment, which comes from atomics, does not reach the result).
+//   combine      out[t] = sum_j weight[t, j] * row[t * top + j] (+ the shared expert's row), float32, in the order of choice.
+//
+// The products exist in two forms: bfloat16 operands on mma.sync tensor-core tiles (float32 accumulation), and a plain
+// float32 form on the CUDA cores (true 32-bit, sums in a fixed order along K) that also takes bfloat16 shapes the first
+// does not.
+#include "common.cuh"
+#include <math.h>
+
+using namespace mi;
+
+namespace {
+
+// ------------------------------------------------------------------ router
+template <typename T>
+__global__ void route_topk_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ router, const float* __restrict__ corr,
+                                  int* __restrict__ chosen, float* __restrict__ weights, int hidden, int E, int top, int g_count,
+                                  int g_keep) {
+    extern __shared__ float rsm[];
+    float* hs = rsm;                       // [hidden]
+    float* s = hs + hidden;                // [E] logits, then softmax scores
+    float* c = s + E;                      // [E] choice scores
+    float* gb = c + E;                     // [E] best choice score per group / kept flags
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const T* row = h + (size_t)t * ldh;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) hs[i] = to_f32(row[i]);
+    __syncthreads();
+    for (int e = warp; e < E; e += nw) {
+        const float* w = router + (size_t)e * hidden;
+        float dot = 0.f;
+        for (int i = lane; i < hidden; i += 32) dot = fmaf(hs[i], w[i], dot);
+        dot = warp_sum(dot);
+        if (lane == 0) s[e] = dot;
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    float mx = -INFINITY, den = 0.f;
+    for (int e = 0; e < E; ++e) mx = fmaxf(mx, s[e]);
+    for (int e = 0; e < E; ++e) { s[e] = expf(s[e] - mx); den += s[e]; }
+    for (int e = 0; e < E; ++e) { s[e] = s[e] / den; c[e] = s[e] + corr[e]; }
+    if (g_count > 0) {
+        const int per = E / g_count;
+        for (int g = 0; g < g_count; ++g) {
+            float b = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, c[e]);
+            gb[g] = b;
+        }
+        // the g_keep best groups: their entry becomes +inf (kept), every other one ends as -inf
+        for (int k = 0; k < g_keep; ++k) {
+            int best = -1;
+            float bv = -INFINITY;
+            for (int g = 0; g < g_count; ++g)
+                if (gb[g] != INFINITY && (best < 0 || gb[g] > bv)) { best = g; bv = gb[g]; }
+            if (best >= 0) gb[best] = INFINITY;
+        }
+        for (int e = 0; e < E; ++e)
+            if (gb[e / per] != INFINITY) c[e] = -INFINITY;
+    }
+    for (int j = 0; j < top; ++j) {
+        int best = -1;
+        float bv = -INFINITY;
+        for (int e = 0; e < E; ++e)
+            if (!isnan(c[e]) && (best < 0 ? c[e] > -INFINITY : c[e] > bv)) { best = e; bv = c[e]; }
+        if (best < 0) best = 0;            // fewer eligible experts than `top`: the configuration reader refuses that
+        chosen[(size_t)t * top + j] = best;
+        weights[(size_t)t * top + j] = s[best];
+        c[best] = NAN;                     // taken
+    }
+}
+
+// ------------------------------------------------------------------ g = min(gate, limit); u = clamp(up); g sigmoid(slope g) (u + 1)
+__device__ __forceinline__ float clamped_glu(float g, float u, float limit, float slope) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-slope * g)) * (u + 1.f);
+}
+
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, float limit, float slope) {
+    const T* row = gu + (size_t)blockIdx.x * 2 * inter;
+    T* o = out + (size_t)blockIdx.x * inter;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x)
+        o[i] = from_f32<T>(clamped_glu(to_f32(row[i]), to_f32(row[inter + i]), limit, slope));
+}
+
+// ------------------------------------------------------------------ sort the pairs by expert
+__global__ void moe_align_kernel(const int* __restrict__ chosen, int P, int E, int BM, int* __restrict__ sorted_pair, int cap_pos,
+                                 int* __restrict__ tile_expert, int cap_tiles) {
+    extern __shared__ int asm_[];
+    int* cnt = asm_;            // [E]
+    int* cur = cnt + E;         // [E]
+    int* off = cur + E;         // [E + 1]
+    for (int e = threadIdx.x; e < E; e += blockDim.x) { cnt[e] = 0; cur[e] = 0; }
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&cnt[chosen[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        off[0] = 0;
+        for (int e = 0; e < E; ++e) off[e + 1] = off[e] + (cnt[e] + BM - 1) / BM * BM;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < cap_pos; i += blockDim.x) sorted_pair[i] = -1;
+    for (int t = threadIdx.x; t < cap_tiles; t += blockDim.x) {
+        const int pos = t * BM;
+        int e = -1;
+        if (pos < off[E]) { e = 0; while (off[e + 1] <= pos) ++e; }
+        tile_expert[t] = e;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        const int e = chosen[p];
+        sorted_pair[off[e] + atomicAdd(&cur[e], 1)] = p;
+    }
+}
+
+// ------------------------------------------------------------------ grouped product, CUDA cores, float32 sums in k order
+// MODE 0 ("in"):  row pos reads A[sorted_pair[pos] / top], W = [E, 2 N, K] (gate rows, then up rows), out[pos, n] = act(gate, up)
+// MODE 1 ("out"): row pos reads A[pos], W = [E, N, K], out[sorted_pair[pos], n]
+constexpr int SM_ = 32, SN_ = 64, SK_ = 32;
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) moe_gemm_simt_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, T* __restrict__ out, int ldo,
+                                                            const int* __restrict__ sorted_pair, const int* __restrict__ tile_expert,
+                                                            int top, int N, int K, float limit, float slope) {
+    const int e = tile_expert[blockIdx.x];
+    if (e < 0) return;
+    __shared__ float As[SM_][SK_ + 1], Bs[SN_][SK_ + 1], Bu[MODE == 0 ? SN_ : 1][SK_ + 1];
+    __shared__ int pair_s[SM_];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int pos0 = blockIdx.x * SM_, n0 = blockIdx.y * SN_;
+    if (tid < SM_) pair_s[tid] = sorted_pair[pos0 + tid];
+    __syncthreads();
+    const T* We = W + (size_t)e * (MODE == 0 ? 2 : 1) * N * K;
+    float acc[2][4] = {}, accu[2][4] = {};
+    for (int k0 = 0; k0 < K; k0 += SK_) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = tid + i * 256, r = idx >> 5, c = idx & 31, pr = pair_s[r];
+            const long long src = MODE == 0 ? pr / top : pos0 + r;
+            As[r][c] = (pr >= 0 && k0 + c < K) ? to_f32(A[src * lda + k0 + c]) : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int idx = tid + i * 256, r = idx >> 5, c = idx & 31, n = n0 + r;
+            const bool ok = n < N && k0 + c < K;
+            Bs[r][c] = ok ? to_f32(We[(size_t)n * K + k0 + c]) : 0.f;
+            if constexpr (MODE == 0) Bu[r][c] = ok ? to_f32(We[(size_t)(N + n) * K + k0 + c]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < SK_; ++kk) {
+            const float a0 = As[ty][kk], a1 = As[ty + 16][kk];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float b = Bs[tx + 16 * j][kk];
+                acc[0][j] = fmaf(a0, b, acc[0][j]);
+                acc[1][j] = fmaf(a1, b, acc[1][j]);
+                if constexpr (MODE == 0) {
+                    const float u = Bu[tx + 16 * j][kk];
+                    accu[0][j] = fmaf(a0, u, accu[0][j]);
+                    accu[1][j] = fmaf(a1, u, accu[1][j]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = ty + 16 * i, pr = pair_s[r];
+        if (pr < 0) continue;
+        const long long dst = MODE == 0 ? pos0 + r : pr;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx + 16 * j;
+            if (n < N) out[dst * ldo + n] = from_f32<T>(MODE == 0 ? clamped_glu(acc[i][j], accu[i][j], limit, slope) : acc[i][j]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ weighted sum per token
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ rows, const float* __restrict__ weights, const T* __restrict__ shared,
+                                   T* __restrict__ out, int hidden, int top) {
+    const size_t t = blockIdx.x;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < hidden; c += gridDim.y * blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < top; ++j) acc = fmaf(weights[t * top + j], to_f32(rows[(t * top + j) * hidden + c]), acc);
+        if (shared) acc += to_f32(shared[t * hidden + c]);
+        out[t * hidden + c] = from_f32<T>(acc);
+    }
+}
+
+}  // namespace
+
+MI_EXPORT int mi_route_topk(const void* h, int ldh, const float* router, const float* corr, int* chosen, float* weights, int T_, int hidden,
+                            int E, int top, int g_count, int g_keep, int dtype, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    const size_t smem = ((size_t)hidden + 3 * (size_t)E) * sizeof(float);
+    if (smem > 200 * 1024 || top > E || (g_count > 0 && E % g_count)) return -2;
+    if (dtype == MI_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(route_topk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        route_topk_kernel<__nv_bfloat16><<<T_, 128, smem, stream>>>((const __nv_bfloat16*)h, ldh, router, corr, chosen, weights, hidden, E, top, g_count, g_keep);
+    } else {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(route_topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        route_topk_kernel<float><<<T_, 128, smem, stream>>>((const float*)h, ldh, router, corr, chosen, weights, hidden, E, top, g_count, g_keep);
+    }
+    return (int)cudaGetLastError();
+}
+
+MI_EXPORT int mi_clamped_glu(const void* gu, void* out, int rows, int inter, float limit, float slope, int dtype, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    dim3 grid(rows, rows >= 512 ? 1 : min(16, (inter + 255) / 256));
+    if (dtype == MI_BF16) clamped_glu_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, limit, slope);
+    else clamped_glu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, inter, limit, slope);
+    return (int)cudaGetLastError();
+}
+
+// sorted_pair: cap_pos ints, tile_expert: cap_tiles ints; cap_pos = cap_tiles * BM >= P + E * (BM - 1)
+MI_EXPORT int mi_moe_align(const int* chosen, int P, int E, int BM, int* sorted_pair, int cap_pos, int* tile_expert, int cap_tiles,
+                           cudaStream_t stream) {
+    if (P == 0) return 0;
+    if (E > 4096 || cap_pos < cap_tiles * BM) return -2;
+    moe_align_kernel<<<1, 1024, (3 * E + 1) * sizeof(int), stream>>>(chosen, P, E, BM, sorted_pair, cap_pos, tile_expert, cap_tiles);
+    return (int)cudaGetLastError();
+}
+
+MI_EXPORT int mi_moe_tile_rows_simt() { return SM_; }
+
+// mode 0: A = tokens [T, K], W [E, 2 N, K], out [cap_pos, N] activated; mode 1: A = [cap_pos, K], W [E, N, K], out [P, N]
+MI_EXPORT int mi_moe_gemm_simt(const void* A, int lda, const void* W, void* out, int ldo, const int* sorted_pair, const int* tile_expert,
+                               int cap_tiles, int top, int N, int K, float limit, float slope, int mode, int dtype, cudaStream_t stream) {
+    if (cap_tiles == 0) return 0;
+    dim3 grid(cap_tiles, (N + SN_ - 1) / SN_);
+    if (grid.y > 65535) return -2;
+#define GO(T, MODE) moe_gemm_simt_kernel<T, MODE><<<grid, 256, 0, stream>>>((const T*)A, lda, (const T*)W, (T*)out, ldo, sorted_pair, tile_expert, \
+                                                                           top, N, K, limit, slope)
+    if (dtype == MI_BF16) { if (mode == 0) GO(__nv_bfloat16, 0); else GO(__nv_bfloat16, 1); }
+    else { if (mode == 0) GO(float, 0); else GO(float, 1); }
+#undef GO
+    return (int)cudaGetLastError();
+}
+
+MI_EXPORT int mi_moe_combine(const void* rows, const float* weights, const void* shared, void* out, int T_, int hidden, int top, int dtype,
+                             cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    dim3 grid(T_, T_ >= 512 ? 1 : min(8, (hidden + 255) / 256));
+    if (dtype == MI_BF16)
+        moe_combine_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)rows, weights, (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, hidden, top);
+    else
+        moe_combine_kernel<float><<<grid, 256, 0, stream>>>((const float*)rows, weights, (const float*)shared, (float*)out, hidden, top);
+    return (int)cudaGetLastError();
+}

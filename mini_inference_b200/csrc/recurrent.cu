@@ -270,6 +270,34 @@ __global__ void silu_f32_kernel(const T* __restrict__ p, int ldp, float* __restr
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) o[i] = silu(to_f32(row[i]));
 }
 
+// ------------------------------------------------------------------ retention prologue: rotate q and k, scale k, all to float32
+// p [T, ldp] = q [H D] | k [H D] | v [H V].  The first 2 * half coordinates of every q and k head are turned in the
+// rotate-half layout (coordinate i pairs with i + half; angle = position * inv_freq[i], float32), the rest pass;
+// k is then multiplied by k_scale.  out [T, 2 H D + H V] float32.
+template <typename T>
+__global__ void rotate_f32_kernel(const T* __restrict__ p, int ldp, float* __restrict__ out, const int* __restrict__ positions,
+                                  const float* __restrict__ inv_freq, int half, float k_scale, int H, int D, int V) {
+    const T* row = p + (size_t)blockIdx.x * ldp;
+    const int HD = H * D, n = 2 * HD + H * V;
+    float* o = out + (size_t)blockIdx.x * n;
+    const float pos = (float)positions[blockIdx.x];
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) {
+        float v = to_f32(row[i]);
+        if (i < 2 * HD) {
+            const int d = i % D;
+            if (d < 2 * half) {
+                const bool low = d < half;
+                const float other = to_f32(row[low ? i + half : i - half]);
+                float sn, cs;
+                sincosf(pos * inv_freq[low ? d : d - half], &sn, &cs);
+                v = low ? v * cs - other * sn : v * cs + other * sn;
+            }
+            if (i >= HD) v *= k_scale;
+        }
+        o[i] = v;
+    }
+}
+
 // ------------------------------------------------------------------ delta-rule prologue, one block per (token, unit)
 // p [T, ldp]: q | k | v (C = 2 KV D + H V channels that pass the convolution) | beta logits [H] | ...
 // a [T, lda]: decay logits [H D].  conv [C, taps], the last tap multiplies the current token.  The inputs of the
@@ -353,6 +381,22 @@ MI_EXPORT int mi_lightning_scan(const void* p, int ldp, float* prep, const float
     dim3 pgrid(T_, T_ >= 256 ? 1 : min(8, (n + 255) / 256));
     if (dtype == MI_BF16) silu_f32_kernel<__nv_bfloat16><<<pgrid, 256, 0, stream>>>((const __nv_bfloat16*)p, ldp, prep, n);
     else silu_f32_kernel<float><<<pgrid, 256, 0, stream>>>((const float*)p, ldp, prep, n);
+    int err = (int)cudaGetLastError();
+    if (err) return err;
+    ScanLayout L{n, 0, H * D, 2 * H * D, 0, 0};
+    return launch_scan<false>(prep, L, decay, state, state_stride, out, seg_q_start, seg_slot, T_, num_segs, H, H, D, V, stream);
+}
+
+// p [T, ldp] = q | k | v as projected; inv_freq: half frequencies (nullptr or half = 0: no rotation).  Otherwise as mi_lightning_scan.
+MI_EXPORT int mi_retention_scan(const void* p, int ldp, float* prep, const int* positions, const float* inv_freq, int half, float k_scale,
+                                const float* decay, float* state, long long state_stride, float* out, const int* seg_q_start,
+                                const int* seg_slot, int T_, int num_segs, int H, int D, int V, int dtype, cudaStream_t stream) {
+    if (num_segs == 0 || T_ == 0) return 0;
+    if (2 * half > D) return -2;
+    const int n = 2 * H * D + H * V;
+    dim3 pgrid(T_, T_ >= 256 ? 1 : min(8, (n + 255) / 256));
+    if (dtype == MI_BF16) rotate_f32_kernel<__nv_bfloat16><<<pgrid, 256, 0, stream>>>((const __nv_bfloat16*)p, ldp, prep, positions, inv_freq, inv_freq ? half : 0, k_scale, H, D, V);
+    else rotate_f32_kernel<float><<<pgrid, 256, 0, stream>>>((const float*)p, ldp, prep, positions, inv_freq, inv_freq ? half : 0, k_scale, H, D, V);
     int err = (int)cudaGetLastError();
     if (err) return err;
     ScanLayout L{n, 0, H * D, 2 * H * D, 0, 0};

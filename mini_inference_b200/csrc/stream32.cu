@@ -79,9 +79,11 @@ __global__ void polynorm_kernel(const T* __restrict__ z, const float* __restrict
 // ------------------------------------------------------------------ o / rms(o over a group) * w * sigmoid(gate)
 // grid (tokens, groups).  o float32 [T, groups * gs]; the weight has wlen entries and column c reads w[c % wlen]
 // (one vector per row: wlen = groups * gs; one vector shared by the groups: wlen = gs).
+// w == nullptr: no weight.  act 0: sigmoid(gate); 1: silu(gate) = gate * sigmoid(gate).
 template <typename TG, typename TY>
 __global__ void group_rmsnorm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, int wlen,
-                                          const TG* __restrict__ gate, int gate_stride, TY* __restrict__ y, int groups, int gs, float eps) {
+                                          const TG* __restrict__ gate, int gate_stride, TY* __restrict__ y, int groups, int gs, float eps,
+                                          int act) {
     __shared__ float scratch[32];
     const size_t t = blockIdx.x;
     const int c0 = blockIdx.y * gs;
@@ -92,8 +94,11 @@ __global__ void group_rmsnorm_gate_kernel(const float* __restrict__ o, const flo
     const TG* grow = gate + t * gate_stride + c0;
     TY* yrow = y + t * groups * gs + c0;
     for (int i = threadIdx.x; i < gs; i += NT) {
-        const float sg = 1.f / (1.f + expf(-to_f32(grow[i])));
-        yrow[i] = from_f32<TY>(orow[i] * r * w[(c0 + i) % wlen] * sg);
+        const float gv = to_f32(grow[i]);
+        float sg = 1.f / (1.f + expf(-gv));
+        if (act == 1) sg *= gv;
+        const float wv = w ? w[(c0 + i) % wlen] : 1.f;
+        yrow[i] = from_f32<TY>(orow[i] * r * wv * sg);
     }
 }
 
@@ -108,7 +113,108 @@ __global__ void head_gate_kernel(const T* __restrict__ o, const T* __restrict__ 
     for (int i = threadIdx.x; i < V; i += blockDim.x) dst[i] = from_f32<T>(to_f32(src[i]) * sg);
 }
 
+// ------------------------------------------------------------------ embedding -> float32 stream (+ its rows in the table's type)
+template <typename T>
+__global__ void embed_stream_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ x, T* __restrict__ rows,
+                                    int hidden, int vocab) {
+    int id = ids[blockIdx.x];
+    if (id < 0 || id >= vocab) id = 0;
+    const T* src = table + (size_t)id * hidden;
+    float* dst = x + (size_t)blockIdx.x * hidden;
+    T* r = rows ? rows + (size_t)blockIdx.x * hidden : nullptr;
+    for (int i = threadIdx.x; i < hidden; i += NT) { const T v = src[i]; dst[i] = to_f32(v); if (r) r[i] = v; }
+}
+
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ x, T* __restrict__ y, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * NT + threadIdx.x; i < n; i += (size_t)gridDim.x * NT) y[i] = from_f32<T>(x[i]);
+}
+
+// ------------------------------------------------------------------ x += mult * ls * (w * y / rms(y)); rows = cast(x)
+// One block per row.  The statistic, the product and the sum are float32; the stream is written back in float32 and,
+// when rows != nullptr, also in the run's type for the sublayer that reads the stream next.
+template <typename TYIN, typename TR>
+__global__ void out_rmsnorm_add_kernel(float* __restrict__ x, const TYIN* __restrict__ y, const float* __restrict__ w,
+                                       const float* __restrict__ ls, float mult, TR* __restrict__ rows, int hidden, float eps) {
+    __shared__ float scratch[32];
+    const size_t r = blockIdx.x;
+    const TYIN* yr = y + r * hidden;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += NT) { const float v = to_f32(yr[i]); ss += v * v; }
+    const float s = rsqrtf(bsum(ss, scratch) / hidden + eps);
+    float* xr = x + r * hidden;
+    for (int i = threadIdx.x; i < hidden; i += NT) {
+        float n = to_f32(yr[i]) * s * w[i];
+        if (ls) n *= ls[i];
+        const float v = xr[i] + mult * n;
+        xr[i] = v;
+        if (rows) rows[r * hidden + i] = from_f32<TR>(v);
+    }
+}
+
+// ------------------------------------------------------------------ (x += delta;) y = w * x / rms(x), x a float32 stream
+template <typename TD, typename TY>
+__global__ void stream_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, const float* __restrict__ w,
+                                      TY* __restrict__ y, const int* __restrict__ rows, int hidden, float eps) {
+    __shared__ float scratch[32];
+    const size_t r = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
+    float* xr = x + r * hidden;
+    const TD* dr = delta ? delta + r * hidden : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += NT) {
+        float v = xr[i];
+        if (dr) v += to_f32(dr[i]);
+        ss += v * v;
+    }
+    const float s = rsqrtf(bsum(ss, scratch) / hidden + eps);
+    TY* yr = y + (size_t)blockIdx.x * hidden;
+    for (int i = threadIdx.x; i < hidden; i += NT) {
+        float v = xr[i];
+        if (dr) v += to_f32(dr[i]);
+        if (dr && !rows) xr[i] = v;
+        yr[i] = from_f32<TY>(v * s * w[i]);
+    }
+}
+
 }  // namespace
+
+MI_EXPORT int mi_embed_stream(const int* ids, const void* table, float* x, void* rows, int T_, int hidden, int vocab, int dtype,
+                              cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    if (dtype == MI_BF16) embed_stream_kernel<__nv_bfloat16><<<T_, NT, 0, stream>>>(ids, (const __nv_bfloat16*)table, x, (__nv_bfloat16*)rows, hidden, vocab);
+    else embed_stream_kernel<float><<<T_, NT, 0, stream>>>(ids, (const float*)table, x, (float*)rows, hidden, vocab);
+    return (int)cudaGetLastError();
+}
+
+MI_EXPORT int mi_cast_rows(const float* x, void* y, long long n, int dtype, cudaStream_t stream) {
+    if (n == 0) return 0;
+    if (dtype != MI_BF16) return -1;
+    const int blocks = (int)((n + NT * 8 - 1) / (NT * 8) < 1184 ? (n + NT * 8 - 1) / (NT * 8) : 1184);
+    cast_rows_kernel<__nv_bfloat16><<<blocks, NT, 0, stream>>>(x, (__nv_bfloat16*)y, (size_t)n);
+    return (int)cudaGetLastError();
+}
+
+// y: [n, hidden] in y_dtype; rows: nullptr or [n, hidden] bfloat16
+MI_EXPORT int mi_out_rmsnorm_add(float* x, const void* y, const float* w, const float* ls, float mult, void* rows, int n, int hidden,
+                                 float eps, int y_dtype, cudaStream_t stream) {
+    if (n == 0) return 0;
+    if (y_dtype == MI_BF16) out_rmsnorm_add_kernel<__nv_bfloat16, __nv_bfloat16><<<n, NT, 0, stream>>>(x, (const __nv_bfloat16*)y, w, ls, mult, (__nv_bfloat16*)rows, hidden, eps);
+    else out_rmsnorm_add_kernel<float, __nv_bfloat16><<<n, NT, 0, stream>>>(x, (const float*)y, w, ls, mult, (__nv_bfloat16*)rows, hidden, eps);
+    return (int)cudaGetLastError();
+}
+
+MI_EXPORT int mi_stream_rmsnorm(float* x, const void* delta, const float* w, void* y, const int* rows, int n, int hidden, float eps,
+                                int delta_dtype, int y_dtype, cudaStream_t stream) {
+    if (n == 0) return 0;
+#define GO(TD, TY) stream_rmsnorm_kernel<TD, TY><<<n, NT, 0, stream>>>(x, (const TD*)delta, w, (TY*)y, rows, hidden, eps)
+    if (delta_dtype == MI_BF16 && y_dtype == MI_BF16) GO(__nv_bfloat16, __nv_bfloat16);
+    else if (delta_dtype == MI_F32 && y_dtype == MI_F32) GO(float, float);
+    else if (delta_dtype == MI_F32 && y_dtype == MI_BF16) GO(float, __nv_bfloat16);
+    else if (delta_dtype == MI_BF16 && y_dtype == MI_F32) GO(__nv_bfloat16, float);
+    else return -1;
+#undef GO
+    return (int)cudaGetLastError();
+}
 
 MI_EXPORT int mi_embed_scaled_norm(const int* ids, const void* table, const float* g, void* x, int T_, int hidden, int vocab,
                                    float eps, int table_dtype, int x_dtype, cudaStream_t stream) {
@@ -143,15 +249,15 @@ MI_EXPORT int mi_polynorm(const void* z, const float* coef, void* out, int rows,
 }
 
 MI_EXPORT int mi_group_rmsnorm_gate(const float* o, const float* w, int wlen, const void* gate, int gate_stride, void* y,
-                                    int T_, int groups, int gs, float eps, int dtype, cudaStream_t stream) {
+                                    int T_, int groups, int gs, float eps, int dtype, int act, cudaStream_t stream) {
     if (T_ == 0) return 0;
     if (groups > 65535) return -2;
     dim3 grid(T_, groups);
     if (dtype == MI_BF16)
         group_rmsnorm_gate_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, NT, 0, stream>>>(o, w, wlen, (const __nv_bfloat16*)gate, gate_stride,
-                                                                                         (__nv_bfloat16*)y, groups, gs, eps);
+                                                                                         (__nv_bfloat16*)y, groups, gs, eps, act);
     else
-        group_rmsnorm_gate_kernel<float, float><<<grid, NT, 0, stream>>>(o, w, wlen, (const float*)gate, gate_stride, (float*)y, groups, gs, eps);
+        group_rmsnorm_gate_kernel<float, float><<<grid, NT, 0, stream>>>(o, w, wlen, (const float*)gate, gate_stride, (float*)y, groups, gs, eps, act);
     return (int)cudaGetLastError();
 }
 

@@ -129,6 +129,8 @@ class CudaOps:
         # round the softmax weights to bfloat16 before the weighted sum; a design that asks for float32 weights gets the
         # float32 kernels of csrc/attention_latent.cu unless MI_LATENT_TC=1 (or this flag) says otherwise.
         self.latent_tc = os.environ.get("MI_LATENT_TC", "0") == "1"
+        # the grouped products of routed experts on mma.sync tensor-core tiles (bfloat16); MI_MOE_TC=0: the CUDA-core form
+        self.moe_tc = os.environ.get("MI_MOE_TC", "1") == "1" and hasattr(self.lib, "mi_moe_gemm_tc")
         self.launches = 0                    # kernels of this package launched so far
 
     def _stream(self):
@@ -630,14 +632,16 @@ class CudaOps:
         self.launches += 1
         return out
 
-    def group_rmsnorm_gate(self, o, weight, gate, eps, groups, gs, out_dtype):
-        """o float32 [T, groups * gs] -> o / rms(o over each group) * weight * sigmoid(gate) in out_dtype.  weight has
-        groups * gs entries (one vector for the row) or gs (shared by the groups); gate [T, groups * gs] may be a strided view."""
+    def group_rmsnorm_gate(self, o, weight, gate, eps, groups, gs, out_dtype, act="sigmoid"):
+        """o float32 [T, groups * gs] -> o / rms(o over each group) * weight * act(gate) in out_dtype.  weight has
+        groups * gs entries (one vector for the row), gs (shared by the groups) or is None (no weight); gate [T, groups * gs]
+        may be a strided view; act: "sigmoid" or "silu"."""
         T = o.shape[0]
         assert o.dtype == torch.float32 and o.is_contiguous() and gate.stride(1) == 1 and gate.dtype == out_dtype
         y = torch.empty((T, groups * gs), dtype=out_dtype, device=o.device)
-        _check(self.lib.mi_group_rmsnorm_gate(_p(o), _p(weight), weight.numel(), _p(gate), gate.stride(0), _p(y), T, groups, gs,
-                                              _c.c_float(eps), _code(out_dtype), self._stream()), "group_rmsnorm_gate")
+        _check(self.lib.mi_group_rmsnorm_gate(_p(o), _p(weight), 1 if weight is None else weight.numel(), _p(gate), gate.stride(0), _p(y),
+                                              T, groups, gs, _c.c_float(eps), _code(out_dtype), {"sigmoid": 0, "silu": 1}[act],
+                                              self._stream()), "group_rmsnorm_gate")
         self.launches += 1
         return y
 
@@ -760,6 +764,163 @@ class CudaOps:
                                              meta.max_pages, _c.c_longlong(hs), _c.c_longlong(ts), H, C, R, meta.page_size, S,
                                              _c.c_float(scale), code, self._stream()), "latent_decode")
             self.launches += 2 if S > 1 else 1
+        return out
+
+    # ---------------------------------------------------------------- float32 stream with norms on the sublayers' outputs
+    def embed_stream(self, ids, table, rows_dtype):
+        """(x, rows): x float32 [T, hidden] = table[ids], the start of a float32 residual stream, and the same rows in the
+        run's dtype (x itself in a float32 run)."""
+        T, hidden = ids.shape[0], table.shape[1]
+        x = torch.empty((T, hidden), dtype=torch.float32, device=table.device)
+        rows = None if rows_dtype == torch.float32 else torch.empty((T, hidden), dtype=table.dtype, device=table.device)
+        assert table.dtype == rows_dtype
+        _check(self.lib.mi_embed_stream(_p(ids), _p(table), _p(x), _p(rows), T, hidden, table.shape[0], _code(table.dtype),
+                                        self._stream()), "embed_stream")
+        self.launches += 1
+        return x, (x if rows is None else rows)
+
+    def cast_rows(self, x, dtype):
+        assert x.dtype == torch.float32 and x.is_contiguous()
+        y = torch.empty(x.shape, dtype=dtype, device=x.device)
+        _check(self.lib.mi_cast_rows(_p(x), _p(y), _c.c_longlong(x.numel()), _code(dtype), self._stream()), "cast_rows")
+        self.launches += 1
+        return y
+
+    def out_rmsnorm_add(self, x, y, weight, scale, mult, eps, rows_dtype):
+        """x (float32 stream, in place) += mult * scale * (weight * y / rms(y)); scale None: no layer scale.  Returns x's rows in
+        rows_dtype (x itself when that is float32)."""
+        assert x.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and y.shape == x.shape
+        rows = None if rows_dtype == torch.float32 else torch.empty(x.shape, dtype=rows_dtype, device=x.device)
+        _check(self.lib.mi_out_rmsnorm_add(_p(x), _p(y), _p(weight), _p(scale), _c.c_float(mult), _p(rows), x.shape[0], x.shape[1],
+                                           _c.c_float(eps), _code(y.dtype), self._stream()), "out_rmsnorm_add")
+        self.launches += 1
+        return x if rows is None else rows
+
+    def stream_rmsnorm(self, x, delta, weight, eps, rows, out_dtype):
+        """x (float32 stream) += delta if given; y = weight * x / rms(x) in out_dtype.  rows: only these rows, stream untouched."""
+        assert x.dtype == torch.float32 and x.is_contiguous() and (delta is None or delta.is_contiguous())
+        hidden = x.shape[-1]
+        n = x.shape[0] if rows is None else rows.shape[0]
+        y = torch.empty((n, hidden), dtype=out_dtype, device=x.device)
+        _check(self.lib.mi_stream_rmsnorm(_p(x), _p(delta), _p(weight), _p(y), _p(rows), n, hidden, _c.c_float(eps),
+                                          _code(delta.dtype if delta is not None else out_dtype), _code(out_dtype), self._stream()),
+               "stream_rmsnorm")
+        self.launches += 1
+        return y
+
+    # ---------------------------------------------------------------- attention with a block mask, a sink and unit-norm q, k
+    def unit_qk_cache(self, p, H, KV, D, V, eps, lam, source, meta, k_cache, v_cache):
+        """p [T, H D + KV D + KV V] = q | k | v.  q and k are divided by their root mean square per head (eps None: left as they
+        are), q in place; v becomes (1 - lam) v + lam source when source [T, KV V] (another layer's values, a view is allowed) is
+        given; k and v go to the rows' slots of the caches (None: this layer writes none).  Returns the q view."""
+        T = p.shape[0]
+        assert p.is_contiguous() and p.shape[1] == (H + KV) * D + KV * V
+        assert source is None or (source.stride(1) == 1 and source.dtype == p.dtype and lam is not None)
+        _check(self.lib.mi_unit_qk_cache(_p(p), p.stride(0), _p(source), 0 if source is None else source.stride(0), _p(lam if source is not None else None),
+                                         _p(meta.slots), _p(k_cache), _p(v_cache), T, H, KV, D, V, meta.page_size,
+                                         _c.c_float(eps or 0.0), int(eps is not None), _code(p.dtype), self._stream()), "unit_qk_cache")
+        self.launches += 1
+        return p[:, :H * D]
+
+    def masked_attention(self, q, k_cache, v_cache, meta, H, KV, D, V, scale, block_size, window, sink):
+        """q [T, H D] (a strided view is allowed) over the pages; keys of D and values of V entries; block_size / window / sink as
+        csrc/attention_masked.cu states them.  Scores, weights and sums are float32.  Returns [T, H V]."""
+        T = q.shape[0]
+        assert q.stride(1) == 1
+        out = torch.empty((T, H * V), dtype=q.dtype, device=q.device)
+        code, blk, win = _code(q.dtype), int(block_size or 0), int(window or 0)
+        rows = getattr(meta, "table_rows", None)
+        num_decode, num_tiles = meta.decode_segs.shape[0], meta.prefill_tiles.shape[0]
+        if num_tiles:
+            _check(self.lib.mi_masked_prefill(
+                _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), num_tiles, _p(meta.seg_q_start),
+                _p(meta.seg_pos0), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D, V, meta.page_size, meta.tile,
+                _c.c_float(scale), blk, win, int(bool(sink)), code, self._stream()), "masked_prefill")
+            self.launches += 1
+        if num_decode:
+            reach = meta.max_kv_len if not blk else min(meta.max_kv_len, blk)
+            reach = reach if not win else min(reach, win)
+            S = self.choose_splits(num_decode * math.ceil(H / 4), reach, 2)
+            o_part = lse = None
+            if S > 1:
+                o_part = torch.empty((num_decode, H, S, V), dtype=torch.float32, device=q.device)
+                lse = torch.empty((num_decode, H, S), dtype=torch.float32, device=q.device)
+            _check(self.lib.mi_masked_decode(
+                _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(o_part), _p(lse), _p(meta.decode_segs), num_decode,
+                _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D, V,
+                meta.page_size, S, _c.c_float(scale), blk, win, int(bool(sink)), code, self._stream()), "masked_decode")
+            self.launches += 2 if S > 1 else 1
+        return out
+
+    # ---------------------------------------------------------------- retention
+    def retention_scan(self, p, H, D, V, inv_freq, k_scale, decay, state, batch):
+        """p [T, >= 2 H D + H V] = q | k | v as projected.  q and k are rotated (rotate-half over the first 2 * len(inv_freq)
+        coordinates of each head; inv_freq None: not at all), k is multiplied by k_scale, all in float32; then
+        S <- decay_h S + k v^T, o = S^T q from the slot's state, which receives the new one.  Returns float32 [T, H V]."""
+        T = p.shape[0]
+        assert p.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
+        out = torch.empty((T, H * V), dtype=torch.float32, device=p.device)
+        prep = torch.empty((T, 2 * H * D + H * V), dtype=torch.float32, device=p.device)
+        half = 0 if inv_freq is None else inv_freq.numel()
+        _check(self.lib.mi_retention_scan(_p(p), p.stride(0), _p(prep), _p(batch.positions), _p(inv_freq), half, _c.c_float(k_scale),
+                                          _p(decay), _p(state), _c.c_longlong(state.stride(0)), _p(out), _p(batch.seg_q_start),
+                                          _p(batch.seg_slot), T, batch.num_segs, H, D, V, _code(p.dtype), self._stream()),
+               "retention_scan")
+        self.launches += 2
+        return out
+
+    # ---------------------------------------------------------------- routed experts
+    def route_topk(self, h, router, correction, top, groups):
+        """(chosen int32 [T, top], weights float32 [T, top]).  router float32 [E, hidden], correction float32 [E]; groups None or
+        (count, keep).  Logits, softmax and the choice are float32 (csrc/moe.cu)."""
+        T, E = h.shape[0], router.shape[0]
+        assert h.stride(1) == 1 and router.dtype == torch.float32 and router.is_contiguous() and correction.dtype == torch.float32
+        chosen = torch.empty((T, top), dtype=torch.int32, device=h.device)
+        weights = torch.empty((T, top), dtype=torch.float32, device=h.device)
+        count, keep = groups if groups else (0, 0)
+        _check(self.lib.mi_route_topk(_p(h), h.stride(0), _p(router), _p(correction), _p(chosen), _p(weights), T, h.shape[1], E, top,
+                                      count, keep, _code(h.dtype), self._stream()), "route_topk")
+        self.launches += 1
+        return chosen, weights
+
+    def clamped_glu(self, gu, limit, slope):
+        """[g | u] -> min(g, limit) * sigmoid(slope * min(g, limit)) * (clamp(u, -limit, limit) + 1)."""
+        rows, inter = gu.shape[0], gu.shape[1] // 2
+        assert gu.is_contiguous()
+        out = torch.empty((rows, inter), dtype=gu.dtype, device=gu.device)
+        _check(self.lib.mi_clamped_glu(_p(gu), _p(out), rows, inter, _c.c_float(limit), _c.c_float(slope), _code(gu.dtype),
+                                       self._stream()), "clamped_glu")
+        self.launches += 1
+        return out
+
+    def expert_ffn(self, h, chosen, weights, w_in, w_out, limit, slope, shared):
+        """sum_j weights[t, j] * expert_{chosen[t, j]}(h[t]) (+ shared[t]).  w_in [E, 2 F, hidden] (gate rows | up rows),
+        w_out [E, hidden, F].  The (token, choice) pairs are sorted by expert on the device; two grouped products run over the
+        sorted rows, the first with the clamped gated activation in its epilogue; nothing returns to the host."""
+        T, top = chosen.shape
+        E, F2, K = w_in.shape
+        F, hidden = F2 // 2, w_out.shape[1]
+        assert h.stride(1) == 1 and w_in.is_contiguous() and w_out.is_contiguous() and K == h.shape[1] and w_in.dtype == h.dtype
+        P, code, dev = T * top, _code(h.dtype), h.device
+        tc = h.dtype == torch.bfloat16 and self.moe_tc and K % 32 == 0 and F % 32 == 0 and h.stride(0) % 8 == 0
+        BM = int(self.lib.mi_moe_tile_rows_tc(P, E) if tc else self.lib.mi_moe_tile_rows_simt())
+        cap_tiles = (P + BM - 1) // BM + min(E, P)
+        cap_pos = cap_tiles * BM
+        sorted_pair = torch.empty(cap_pos, dtype=torch.int32, device=dev)
+        tile_expert = torch.empty(cap_tiles, dtype=torch.int32, device=dev)
+        _check(self.lib.mi_moe_align(_p(chosen), P, E, BM, _p(sorted_pair), cap_pos, _p(tile_expert), cap_tiles, self._stream()), "moe_align")
+        y = torch.empty((cap_pos, F), dtype=h.dtype, device=dev)
+        rows = torch.empty((P, hidden), dtype=h.dtype, device=dev)
+        gemm = self.lib.mi_moe_gemm_tc if tc else self.lib.mi_moe_gemm_simt
+        extra = (BM,) if tc else ()
+        _check(gemm(_p(h), h.stride(0), _p(w_in), _p(y), F, _p(sorted_pair), _p(tile_expert), cap_tiles, top, F, K,
+                    _c.c_float(limit), _c.c_float(slope), 0, *extra, code, self._stream()), "moe_gemm (in)")
+        _check(gemm(_p(y), F, _p(w_out), _p(rows), hidden, _p(sorted_pair), _p(tile_expert), cap_tiles, top, hidden, F,
+                    _c.c_float(limit), _c.c_float(slope), 1, *extra, code, self._stream()), "moe_gemm (out)")
+        out = torch.empty((T, hidden), dtype=h.dtype, device=dev)
+        assert shared is None or (shared.is_contiguous() and shared.shape == out.shape)
+        _check(self.lib.mi_moe_combine(_p(rows), _p(weights), _p(shared), _p(out), T, hidden, top, code, self._stream()), "moe_combine")
+        self.launches += 4
         return out
 
     # ---------------------------------------------------------------- sampling
