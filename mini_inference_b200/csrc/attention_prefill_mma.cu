@@ -61,7 +61,11 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                         const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ tiles, const int* __restrict__ seg_q_start,
                         const int* __restrict__ seg_pos0, const int* __restrict__ block_table,
-                        const int* __restrict__ table_rows, int table_stride, int H, int KV, int ps, float scale_log2, int window) {
+                        const int* __restrict__ table_rows, int table_stride, int H, int KV, int ps, float scale_log2, int window,
+                        int block, int sink) {
+    // block > 0: a query at p sees only keys of its own block of positions, j >= floor(p / block) * block.  sink: the softmax has
+    // one more term of score 0 without a value: the running maximum starts at 0 and the running sum at 1.
+    auto first_key = [&](int p) { return max(block > 0 ? p / block * block : 0, window > 0 ? p - window + 1 : 0); };
     constexpr int CH = D / 8;               // 16-byte chunks per row
     constexpr int KS = D / 16;              // k-steps of Q K^T
     constexpr int DT = D / 8;               // 8-column output tiles
@@ -81,7 +85,7 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     const int rows = min(BQ, n - r0);
     const int* table_row = block_table + (size_t)(table_rows ? table_rows[seg] : seg) * table_stride;
     const int p_first = pos0 + r0, p_last = pos0 + r0 + rows - 1;
-    const int kt_lo = window > 0 ? max(0, p_first - window + 1) / BK : 0;
+    const int kt_lo = first_key(p_first) / BK;
     const int kt_hi = p_last / BK;                                          // inclusive
 
     // ---- loads
@@ -111,7 +115,7 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     float o[DT][4];
 #pragma unroll
     for (int t = 0; t < DT; ++t) { o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f; }
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float m0 = sink ? 0.f : -INFINITY, m1 = m0, l0 = sink && c == 0 ? 1.f : 0.f, l1 = l0;      // a row's sum is spread over four lanes
     const int p_row0 = pos0 + r0 + warp * 16 + g, p_row1 = p_row0 + 8;     // positions of this thread's two rows
 
     cp_async_wait<0>();
@@ -143,7 +147,8 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
             }
         // ---- mask + online softmax (base 2); a tile wholly inside every row's visible range needs no mask
         float mx0 = -INFINITY, mx1 = -INFINITY;
-        const bool inside = kt * BK + BK - 1 <= p_row0 - g && (window <= 0 || kt * BK > p_row0 - g + 15 - window);
+        const bool inside = kt * BK + BK - 1 <= p_row0 - g && kt * BK >= first_key(p_row0 - g + 15);
+        const int lo_row0 = first_key(p_row0), lo_row1 = first_key(p_row1);
         if (inside) {
 #pragma unroll
             for (int nt = 0; nt < BK / 8; ++nt) {
@@ -158,8 +163,8 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int j = kt * BK + nt * 8 + 2 * c + e;
-                    const bool ok0 = j <= p_row0 && (window <= 0 || j > p_row0 - window);
-                    const bool ok1 = j <= p_row1 && (window <= 0 || j > p_row1 - window);
+                    const bool ok0 = j <= p_row0 && j >= lo_row0;
+                    const bool ok1 = j <= p_row1 && j >= lo_row1;
                     s[nt][e] = ok0 ? s[nt][e] * scale_log2 : -INFINITY;
                     s[nt][2 + e] = ok1 ? s[nt][2 + e] * scale_log2 : -INFINITY;
                     mx0 = fmaxf(mx0, s[nt][e]);
@@ -230,7 +235,7 @@ template <bool SPLIT>
 static int prefill_mma_launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                               const int* tiles, int num_tiles, const int* seg_q_start, const int* seg_pos0,
                               const int* block_table, const int* table_rows, int table_stride, int H, int KV, int D, int ps,
-                              int tile_rows, float scale, int window, cudaStream_t stream) {
+                              int tile_rows, float scale, int window, int block, int sink, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     if ((D != 64 && D != 128) || H % KV || tile_rows != BQ || q_stride % 8) return -2;
     static bool configured[2] = {false, false};
@@ -245,7 +250,7 @@ static int prefill_mma_launch(const void* q, int q_stride, const void* k_cache, 
         } \
         attn_prefill_mma_kernel<DD, SPLIT><<<grid, PF_WARPS * 32, smem, stream>>>( \
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
-            (__nv_bfloat16*)out, tiles, seg_q_start, seg_pos0, block_table, table_rows, table_stride, H, KV, ps, scale_log2, window); \
+            (__nv_bfloat16*)out, tiles, seg_q_start, seg_pos0, block_table, table_rows, table_stride, H, KV, ps, scale_log2, window, block, sink); \
     } while (0)
     if (D == 128) LAUNCH(128, 0); else LAUNCH(64, 1);
 #undef LAUNCH
@@ -257,7 +262,7 @@ MI_EXPORT int mi_attn_prefill_mma(const void* q, int q_stride, const void* k_cac
                                   const int* block_table, const int* table_rows, int table_stride, int H, int KV, int D, int ps,
                                   int tile_rows, float scale, int window, cudaStream_t stream) {
     return prefill_mma_launch<false>(q, q_stride, k_cache, v_cache, out, tiles, num_tiles, seg_q_start, seg_pos0, block_table, table_rows,
-                                     table_stride, H, KV, D, ps, tile_rows, scale, window, stream);
+                                     table_stride, H, KV, D, ps, tile_rows, scale, window, 0, 0, stream);
 }
 
 // The same with every softmax weight split into two bfloat16 numbers for the P V product (see SPLIT above).
@@ -266,5 +271,14 @@ MI_EXPORT int mi_attn_prefill_mma_split(const void* q, int q_stride, const void*
                                         const int* block_table, const int* table_rows, int table_stride, int H, int KV, int D, int ps,
                                         int tile_rows, float scale, int window, cudaStream_t stream) {
     return prefill_mma_launch<true>(q, q_stride, k_cache, v_cache, out, tiles, num_tiles, seg_q_start, seg_pos0, block_table, table_rows,
-                                    table_stride, H, KV, D, ps, tile_rows, scale, window, stream);
+                                    table_stride, H, KV, D, ps, tile_rows, scale, window, 0, 0, stream);
+}
+
+// Split weights, and the mask and softmax of csrc/attention_masked.cu: blocks of positions (block > 0), a sink term (sink != 0).
+MI_EXPORT int mi_attn_prefill_mma_masked(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                         const int* tiles, int num_tiles, const int* seg_q_start, const int* seg_pos0,
+                                         const int* block_table, const int* table_rows, int table_stride, int H, int KV, int D, int ps,
+                                         int tile_rows, float scale, int window, int block, int sink, cudaStream_t stream) {
+    return prefill_mma_launch<true>(q, q_stride, k_cache, v_cache, out, tiles, num_tiles, seg_q_start, seg_pos0, block_table, table_rows,
+                                    table_stride, H, KV, D, ps, tile_rows, scale, window, block, sink, stream);
 }

@@ -191,6 +191,130 @@ __global__ void __launch_bounds__(256) moe_gemm_simt_kernel(const T* __restrict_
     }
 }
 
+// ------------------------------------------------------------------ grouped product, bfloat16 on mma.sync tiles
+// A block of 8 warps (WM x WN) owns BM = 16 MT WM sorted rows of ONE expert and 128 rows of the expert's matrix
+// (MODE 1: 128 output columns; MODE 0: 64 gate rows and the 64 up rows of the same columns, interleaved per warp so that
+// a thread holds gate and up of the same output in its accumulators).  K runs in steps of 32 through a three-stage
+// cp.async ring; rows of shared memory are padded to 80 bytes, which keeps ldmatrix free of bank conflicts.
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void cp16(uint32_t dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;                                   // 0 bytes read: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" :: "r"(dst), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_commit_group() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait_group() { asm volatile("cp.async.wait_group %0;\n" :: "n"(N) : "memory"); }
+
+constexpr int TK = 32, TROW = 40, TSTAGES = 3;                      // k per stage, padded row (elements), ring depth
+
+template <int MODE, int MT, int WM, int WN>
+__global__ void __launch_bounds__(256) moe_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W,
+                                                          __nv_bfloat16* __restrict__ out, int ldo, const int* __restrict__ sorted_pair,
+                                                          const int* __restrict__ tile_expert, int top, int N, int K, float limit, float slope) {
+    constexpr int BM = 16 * MT * WM, WNE = 128 / WN, NT = WNE / 8, BN_OUT = MODE == 0 ? 64 : 128;
+    const int e = tile_expert[blockIdx.x];
+    if (e < 0) return;
+    extern __shared__ __align__(16) unsigned char tsm[];
+    __nv_bfloat16* sA = reinterpret_cast<__nv_bfloat16*>(tsm);                  // [TSTAGES][BM][TROW]
+    __nv_bfloat16* sB = sA + TSTAGES * BM * TROW;                               // [TSTAGES][128][TROW]
+    int* pair_s = reinterpret_cast<int*>(sB + TSTAGES * 128 * TROW);            // [BM]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, wm = warp / WN, wn = warp % WN;
+    const int pos0 = blockIdx.x * BM, n0 = blockIdx.y * BN_OUT;
+    for (int i = tid; i < BM; i += 256) pair_s[i] = sorted_pair[pos0 + i];
+    __syncthreads();
+    const __nv_bfloat16* We = W + (size_t)e * (MODE == 0 ? 2 : 1) * N * K;
+    // what this thread copies per stage: chunks of 16 bytes, (row, k chunk)
+    constexpr int A_CH = BM * 4, B_CH = 128 * 4;
+    auto load_stage = [&](int stage, int k0) {
+        for (int c = tid; c < A_CH; c += 256) {
+            const int r = c >> 2, kc = c & 3, pr = pair_s[r];
+            const long long src = MODE == 0 ? pr / top : pos0 + r;
+            cp16((uint32_t)__cvta_generic_to_shared(sA + (stage * BM + r) * TROW + kc * 8), A + (pr >= 0 ? src * lda + k0 + kc * 8 : 0), pr >= 0);
+        }
+        for (int c = tid; c < B_CH; c += 256) {
+            const int r = c >> 2, kc = c & 3;
+            int col, grow;
+            if (MODE == 0) {                                        // warp w's rows: its gate columns, then the up rows of the same columns
+                const int w = r / WNE, rr = r % WNE;
+                col = n0 + w * (WNE / 2) + rr % (WNE / 2);
+                grow = rr < WNE / 2 ? col : N + col;
+            } else {
+                col = n0 + r;
+                grow = col;
+            }
+            const bool ok = col < N;
+            cp16((uint32_t)__cvta_generic_to_shared(sB + (stage * 128 + r) * TROW + kc * 8), We + (ok ? (size_t)grow * K + k0 + kc * 8 : 0), ok);
+        }
+    };
+    float acc[MT][NT][4];
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) acc[i][j][x] = 0.f;
+    const int steps = K / TK;
+    for (int s = 0; s < TSTAGES - 1; ++s) {
+        if (s < steps) load_stage(s, s * TK);
+        cp_commit_group();
+    }
+    for (int it = 0; it < steps; ++it) {
+        cp_wait_group<TSTAGES - 2>();
+        __syncthreads();                                            // stage `it` has landed; everybody is done with stage it - 1
+        if (it + TSTAGES - 1 < steps) load_stage((it + TSTAGES - 1) % TSTAGES, (it + TSTAGES - 1) * TK);
+        cp_commit_group();
+        const __nv_bfloat16* a_s = sA + (it % TSTAGES) * BM * TROW;
+        const __nv_bfloat16* b_s = sB + (it % TSTAGES) * 128 * TROW;
+#pragma unroll
+        for (int k16 = 0; k16 < TK / 16; ++k16) {
+            uint32_t af[MT][4], bfr[NT / 2][4];
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+                ldsm4(af[i], (uint32_t)__cvta_generic_to_shared(a_s + ((wm * MT + i) * 16 + (lane & 15)) * TROW + k16 * 16 + (lane >> 4) * 8));
+#pragma unroll
+            for (int j = 0; j < NT / 2; ++j)
+                ldsm4(bfr[j], (uint32_t)__cvta_generic_to_shared(b_s + (wn * WNE + j * 16 + (lane & 7) + (lane >> 4) * 8) * TROW + k16 * 16 + ((lane >> 3) & 1) * 8));
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+#pragma unroll
+                for (int j = 0; j < NT; ++j) mma16816(acc[i][j], af[i], bfr[j / 2][(j & 1) * 2], bfr[j / 2][(j & 1) * 2 + 1]);
+        }
+    }
+    cp_wait_group<0>();
+    const int g = lane >> 2, c2 = (lane & 3) * 2;
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = (wm * MT + i) * 16 + g + half * 8, pr = pair_s[r];
+            if (pr < 0) continue;
+            __nv_bfloat16* orow = out + (MODE == 0 ? (long long)(pos0 + r) : (long long)pr) * ldo;
+            if (MODE == 0) {
+#pragma unroll
+                for (int j = 0; j < NT / 2; ++j) {
+                    const int col = n0 + wn * (WNE / 2) + j * 8 + c2;
+                    if (col < N) {                                   // N is even: col + 1 < N as well
+                        const float y0 = clamped_glu(acc[i][j][half * 2], acc[i][j + NT / 2][half * 2], limit, slope);
+                        const float y1 = clamped_glu(acc[i][j][half * 2 + 1], acc[i][j + NT / 2][half * 2 + 1], limit, slope);
+                        *reinterpret_cast<__nv_bfloat162*>(orow + col) = __floats2bfloat162_rn(y0, y1);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    const int col = n0 + wn * WNE + j * 8 + c2;
+                    if (col + 1 < N) *reinterpret_cast<__nv_bfloat162*>(orow + col) = __floats2bfloat162_rn(acc[i][j][half * 2], acc[i][j][half * 2 + 1]);
+                    else if (col < N) orow[col] = __float2bfloat16_rn(acc[i][j][half * 2]);
+                }
+            }
+        }
+}
+
 // ------------------------------------------------------------------ weighted sum per token
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ rows, const float* __restrict__ weights, const T* __restrict__ shared,
@@ -250,6 +374,34 @@ MI_EXPORT int mi_moe_gemm_simt(const void* A, int lda, const void* W, void* out,
                                                                            top, N, K, limit, slope)
     if (dtype == MI_BF16) { if (mode == 0) GO(__nv_bfloat16, 0); else GO(__nv_bfloat16, 1); }
     else { if (mode == 0) GO(float, 0); else GO(float, 1); }
+#undef GO
+    return (int)cudaGetLastError();
+}
+
+// rows per tile of the tensor-core form for P pairs over E experts: tall tiles when an expert gets many rows
+MI_EXPORT int mi_moe_tile_rows_tc(int P, int E) {
+    const int avg = (P + E - 1) / E;
+    return avg > 48 ? 128 : avg > 12 ? 64 : 16;
+}
+
+// bfloat16 only; K % 32 == 0, N even, lda % 8 == 0; BM as mi_moe_tile_rows_tc said (and as mi_moe_align sorted)
+MI_EXPORT int mi_moe_gemm_tc(const void* A, int lda, const void* W, void* out, int ldo, const int* sorted_pair, const int* tile_expert,
+                             int cap_tiles, int top, int N, int K, float limit, float slope, int mode, int BM, int dtype, cudaStream_t stream) {
+    if (cap_tiles == 0) return 0;
+    if (dtype != MI_BF16) return -1;
+    if (K % TK || N % 2 || lda % 8 || ldo % 2) return -2;
+    dim3 grid(cap_tiles, (N + (mode == 0 ? 64 : 128) - 1) / (mode == 0 ? 64 : 128));
+    if (grid.y > 65535) return -2;
+    const size_t smem = (size_t)TSTAGES * (BM + 128) * TROW * sizeof(__nv_bfloat16) + BM * sizeof(int);
+#define GO(MODE, MT, WM, WN) do { \
+        auto kern = moe_gemm_tc_kernel<MODE, MT, WM, WN>; \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        kern<<<grid, 256, smem, stream>>>((const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, (__nv_bfloat16*)out, ldo, sorted_pair, \
+                                          tile_expert, top, N, K, limit, slope); } while (0)
+    if (BM == 128) { if (mode == 0) GO(0, 4, 2, 4); else GO(1, 4, 2, 4); }
+    else if (BM == 64) { if (mode == 0) GO(0, 2, 2, 4); else GO(1, 2, 2, 4); }
+    else if (BM == 16) { if (mode == 0) GO(0, 1, 1, 8); else GO(1, 1, 1, 8); }
+    else return -2;
 #undef GO
     return (int)cudaGetLastError();
 }

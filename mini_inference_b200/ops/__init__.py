@@ -831,7 +831,16 @@ class CudaOps:
         code, blk, win = _code(q.dtype), int(block_size or 0), int(window or 0)
         rows = getattr(meta, "table_rows", None)
         num_decode, num_tiles = meta.decode_segs.shape[0], meta.prefill_tiles.shape[0]
-        if num_tiles:
+        if (num_tiles and self.fast_attention and q.dtype == torch.bfloat16 and D == V and D in (64, 128) and meta.tile == 64
+                and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
+            # key and value rows of 64 or 128 entries: the mma.sync prompt kernel, every softmax weight entering P V as two
+            # bfloat16 numbers (float32 scores and softmax, 16 mantissa bits of each weight, float32 sums)
+            _check(self.lib.mi_attn_prefill_mma_masked(
+                _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), num_tiles, _p(meta.seg_q_start),
+                _p(meta.seg_pos0), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D, meta.page_size, meta.tile,
+                _c.c_float(scale), win, blk, int(bool(sink)), self._stream()), "attn_prefill_mma_masked")
+            self.launches += 1
+        elif num_tiles:
             _check(self.lib.mi_masked_prefill(
                 _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), num_tiles, _p(meta.seg_q_start),
                 _p(meta.seg_pos0), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D, V, meta.page_size, meta.tile,
