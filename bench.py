@@ -277,7 +277,7 @@ def reference_arm(args):
 
 
 def design_bench(args):
-    """--design naditar: prompt and decode throughput of the Naditar design at layer sizes of real models (random weights),
+    """--design naditar | namesun: prompt and decode throughput of that design at layer sizes of real models (random weights),
     beside Qwen3 dense of the same width, depth, vocabulary and feed-forward parameters, and every new kernel beside its
     Qwen3 counterpart with its share of the bound it is up against.  One JSON line; the default workload is untouched."""
     import torch
@@ -287,11 +287,12 @@ def design_bench(args):
     from mini_inference_b200.ops import get_ops
 
     pk, vocab = peaks(), 65536
-    out = {"design": "naditar", "peaks": pk, "sizes": {}}
+    design_config, qwen3_config, design_kernels = microbench.DESIGNS[args.design]
+    out = {"design": args.design, "peaks": pk, "sizes": {}}
     for size in args.design_sizes.split(","):
         res = {}
-        for name, cfg in (("naditar", microbench.naditar_config(size, args.design_layers, vocab)),
-                          ("qwen3", microbench.qwen3_config_like(size, args.design_layers, vocab))):
+        for name, cfg in ((args.design, design_config(size, args.design_layers, vocab)),
+                          ("qwen3", qwen3_config(size, args.design_layers, vocab))):
             for tc in ((False, True) if name == "naditar" else (False,)):
                 llm = LLM(None, random_config=cfg, random_seed=0, dtype="bfloat16", device="cuda:0", kv_block_size=16,
                           kv_cache_tokens=64 * args.ctx + 4096, kv_watermark=0.0, max_num_seqs=64, max_model_len=args.ctx,
@@ -312,14 +313,14 @@ def design_bench(args):
         out["sizes"][size] = {"layers": args.design_layers, "ctx": args.ctx, "engines": res}
     if not args.skip_points:
         margs = argparse.Namespace(design_size=args.design_sizes.split(",")[0], tokens=2048, ctx=args.ctx, iters=20)
-        out["kernels"] = microbench.bench_design(margs, get_ops("cuda:0"), pk["hbm_gbs"], out=lambda *a, **k: print(*a, file=sys.stderr, **k))
+        out["kernels"] = design_kernels(margs, get_ops("cuda:0"), pk["hbm_gbs"], out=lambda *a, **k: print(*a, file=sys.stderr, **k))
     print(json.dumps(out))
     return 0
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=["naditar"], help="instead of the default workload: this design beside Qwen3 at equal sizes")
+    ap.add_argument("--design", default=None, choices=["naditar", "namesun"], help="instead of the default workload: this design beside Qwen3 at equal sizes")
     ap.add_argument("--design-sizes", default="2k,4k")
     ap.add_argument("--design-layers", type=int, default=8)
     ap.add_argument("--gpus", type=int, default=1)

@@ -7,6 +7,7 @@ bench/micro/bench_attention.py (:61-167: paged decode attention over batch x con
     python -m mini_inference_b200.cli.microbench attention [--batch 1,8,64] [--ctx 4096]
     python -m mini_inference_b200.cli.microbench prefill   [--tokens 2048] [--ctx-before 0]
     python -m mini_inference_b200.cli.microbench design    [--design-size 2k|4k]   (the Naditar kernels beside Qwen3's)
+    python -m mini_inference_b200.cli.microbench namesun   [--design-size 2k|4k]   (the Namesun kernels beside Qwen3's)
 
 Each line: kernel, shape, microseconds (CUDA events, after warm-up), GB/s of the bytes the
 kernel has to read, and that as a share of the measured copy bandwidth."""
@@ -318,9 +319,169 @@ def bench_design(args, ops, peak, out=print):
     return rows
 
 
+NAMESUN_SIZES = {
+    # width, heads, head sizes and active feed-forward parameters per token in the range of 1-3 B and 7-8 B active-parameter models
+    "2k": dict(width=2048, ff=8192, heads=16, kv_heads=8, dim=128, vdim=128, block=1024, experts=32, top=4, eff=1024, shared=2048, groups=(8, 4)),
+    "4k": dict(width=4096, ff=12288, heads=32, kv_heads=8, dim=128, vdim=128, block=1024, experts=64, top=6, eff=1536, shared=3072, groups=(8, 4)),
+}
+
+
+def namesun_config(size, layers, vocab=65536):
+    z = NAMESUN_SIZES[size]
+    experts = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"][0], "keep": z["groups"][1]}},
+               "expert": {"ff": z["eff"], "limit": 7.0}, "shared": {"ff": z["shared"], "limit": 7.0}}
+    ret = {"type": "retention", "mixer": {"heads": z["heads"], "dim": z["dim"], "vdim": z["vdim"], "rot": {"dims": z["dim"], "base": 1e6},
+                                          "decay": [1.0 - 2.0 ** -(2 + 6 * h / z["heads"]) for h in range(z["heads"])]}}
+    att = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5 * 8,
+                                          "mask": {"size": z["block"]}, "v_mix": True}}
+    pattern = [dict(ret, mlp={"kind": "dense", "ff": z["ff"]}), dict(ret, mlp=experts), dict(att, mlp=experts), dict(ret, mlp=experts)]
+    return {"architecture": "Namesun", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-6}, "residual_mult": 0.3,
+            "layers": [pattern[i % 4] if i else pattern[0] for i in range(layers)]}
+
+
+def qwen3_config_like_namesun(size, layers, vocab=65536):
+    """Qwen3 dense of the same width, depth, vocabulary and heads; its feed-forward holds what a Namesun token uses (top experts + shared)."""
+    z = NAMESUN_SIZES[size]
+    return {"architectures": ["Qwen3ForCausalLM"], "hidden_size": z["width"], "num_hidden_layers": layers, "num_attention_heads": z["heads"],
+            "num_key_value_heads": z["kv_heads"], "head_dim": 128, "intermediate_size": z["top"] * z["eff"] + z["shared"], "vocab_size": vocab,
+            "rope_theta": 1e6, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 40960}
+
+
+def bench_namesun(args, ops, peak, out=print):
+    """Each kernel of the Namesun design at the layer sizes of --design-size beside the like kernel of Qwen3 dense, with the bytes
+    or operations it cannot avoid as a share of its bound (measured copy bandwidth, measured bf16 tensor peak, or, for the
+    float32 recurrence, the float32 FMA rate of the CUDA cores)."""
+    import numpy as np
+    z = NAMESUN_SIZES[args.design_size]
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    bf16_peak = 1590.0
+    if os.path.isfile(os.path.join(here, "MEASURED_PEAKS.json")):
+        with open(os.path.join(here, "MEASURED_PEAKS.json")) as f:
+            bf16_peak = json.load(f)["bf16_tflops"]
+    props = torch.cuda.get_device_properties(0)
+    fma_peak = props.multi_processor_count * 128 * 2 * 1.965e9 / 1e12
+    rows = []
+
+    def line(kernel, shape, us, amount, bound):
+        got, top, unit = {"hbm": (amount / us / 1e3, peak, "GB/s"), "bf16": (amount / us / 1e6, bf16_peak, "TFLOP/s"),
+                          "fma": (amount / us / 1e6, fma_peak, "TFLOP/s (fp32 FMA)")}[bound]
+        rows.append({"kernel": kernel, "shape": shape, "us": round(us, 2), "achieved": round(got, 1), "unit": unit, "frac": round(got / top, 3)})
+        out(f"{kernel:40s} {shape:44s} {us:9.2f} us {got:9.1f} {unit:20s} {100 * got / top:5.1f} % of bound", flush=True)
+
+    t = lambda a: torch.tensor(np.asarray(a, dtype=np.int32), device="cuda")       # noqa: E731
+    bf = torch.bfloat16
+    W, H, KV, D, V = z["width"], z["heads"], z["kv_heads"], z["dim"], z["vdim"]
+    E, top, F, SH = z["experts"], z["top"], z["eff"], z["shared"]
+    T, it = args.tokens, args.iters
+    # ---- stream kernels
+    x, y = torch.randn(4, T, W, device="cuda"), torch.randn(4, T, W, device="cuda", dtype=bf)
+    wn = torch.ones(W, device="cuda")
+    us = timed(lambda i: ops.out_rmsnorm_add(x[i % 4], y[i % 4], wn, wn, 0.3, 1e-6, bf), it)
+    line("output norm + add (f32 stream)", f"T={T} width={W}", us, T * W * 12.0, "hbm")
+    xb, wb = torch.randn(4, T, W, device="cuda", dtype=bf), torch.ones(W, device="cuda", dtype=bf)
+    us = timed(lambda i: ops.add_rmsnorm(xb[i % 4], y[i % 4], wb, 1e-6), it)
+    line("  Qwen3: add + rmsnorm (bf16 stream)", f"T={T} width={W}", us, T * W * 8.0, "hbm")
+    gu = torch.randn(4, T, 2 * SH, device="cuda", dtype=bf)
+    us = timed(lambda i: ops.clamped_glu(gu[i % 4], 7.0, 1.702), it)
+    line("clamped gated activation", f"T={T} inter={SH}", us, T * SH * 6.0, "hbm")
+    us = timed(lambda i: ops.swiglu(gu[i % 4]), it)
+    line("  Qwen3: swiglu", f"T={T} inter={SH}", us, T * SH * 6.0, "hbm")
+    # ---- routed experts beside the dense feed-forward of equal active size
+    for rows_n in (T, 64, 8):
+        h = torch.randn(rows_n, W, device="cuda", dtype=bf)
+        router, corr = torch.randn(E, W, device="cuda") * 0.05, torch.zeros(E, device="cuda")
+        reps = 4 if rows_n > 64 else max(2, (300 << 20) // (E * 3 * F * W * 2) + 1)
+        w_in = torch.randn(reps, E, 2 * F, W, device="cuda", dtype=bf) * 0.02
+        w_out = torch.randn(reps, E, W, F, device="cuda", dtype=bf) * 0.02
+        us = timed(lambda i: ops.route_topk(h, router, corr, top, z["groups"]), it)
+        line("router: logits, softmax, grouped top-k", f"rows={rows_n} experts={E} top={top}", us, rows_n * W * 2.0 + E * W * 4.0, "hbm")
+        chosen, wts = ops.route_topk(h, router, corr, top, z["groups"])
+        us = timed(lambda i: ops.expert_ffn(h, chosen, wts, w_in[i % reps], w_out[i % reps], 7.0, 1.702, None), it)
+        flops = 2.0 * rows_n * top * 3 * F * W
+        hit = min(E, rows_n * top)                                   # experts that can be hit at all
+        if rows_n > 64:
+            line("experts: sort, 2 grouped products, sum", f"rows={rows_n} experts={E} top={top} ff={F}", us, flops, "bf16")
+        else:
+            line("experts: sort, 2 grouped products, sum", f"rows={rows_n} experts={E} top={top} ff={F}", us, hit * 3.0 * F * W * 2, "hbm")
+        inter = top * F
+        wg, wd = torch.randn(reps, 2 * inter, W, device="cuda", dtype=bf) * 0.02, torch.randn(reps, W, inter, device="cuda", dtype=bf) * 0.02
+        us = timed(lambda i: ops.linear(ops.gated_linear(h, wg[i % reps]), wd[i % reps]), it)
+        if rows_n > 64:
+            line("  Qwen3: gate/up + swiglu + down", f"rows={rows_n} inter={inter}", us, flops, "bf16")
+        else:
+            line("  Qwen3: gate/up + swiglu + down", f"rows={rows_n} inter={inter}", us, 3.0 * inter * W * 2, "hbm")
+        del w_in, w_out, wg, wd
+    # ---- retention: one prompt of T tokens; decode steps of B requests
+    inv = (1e6 ** (-torch.arange(0, D, 2, dtype=torch.float64) / D)).float().cuda()
+    for B, n in ((1, T), (8, 1), (64, 1)):
+        rows_n = B * n
+        batch = types.SimpleNamespace(seg_q_start=t(np.arange(B + 1) * n), seg_slot=t(np.arange(B) + 1), num_segs=B,
+                                      positions=t(np.tile(np.arange(n), B) if n > 1 else np.full(B, 4095)))
+        shape = f"{'prompt' if n > 1 else 'decode'} B={B} T={n} heads={H} {D}x{V}"
+        reps = 4 if n > 1 else max(2, (256 << 20) // (B * H * D * V * 4) + 1)
+        p = torch.randn(rows_n, 2 * H * D + 2 * H * V, device="cuda", dtype=bf)
+        decay = torch.full((H,), 0.99, device="cuda")
+        st = torch.zeros(reps, B + 1, H * D * V, device="cuda")
+        us = timed(lambda i: ops.retention_scan(p, H, D, V, inv, D ** -0.5, decay, st[i % reps], batch), it)
+        line("retention: rotation + scan", shape, us, 4.0 * H * D * V * rows_n if n > 1 else 8.0 * B * H * D * V, "fma" if n > 1 else "hbm")
+        del st
+    # ---- attention inside blocks beside causal attention
+    ps, blk = 16, z["block"]
+    pages = -(-T // ps)
+    table = (torch.randperm(pages, device="cuda").to(torch.int32) + 1).view(1, pages).contiguous()
+    tiles = dict(prefill_tiles=t([(0, r) for r in range(0, T, 64)]).view(-1, 2), prefill_tiles2=t([(0, r) for r in range(0, T, 128)]).view(-1, 2))
+    meta = types.SimpleNamespace(page_size=ps, tile=64, block_table=table, table_rows=t([0]), max_pages=pages, seg_q_start=t([0, T]), seg_pos0=t([0]),
+                                 seg_kv_len=t([T]), decode_segs=t([]), max_kv_len=T, num_tokens=T, positions=t(np.arange(T)),
+                                 slots=t(np.arange(T) + ps), **tiles)
+    kv = torch.randn(4, 2, pages + 1, KV, ps, D, device="cuda", dtype=bf)
+    qq = torch.randn(T, H * D, device="cuda", dtype=bf)
+    pairs_blk = sum((p % blk) + 1 for p in range(T))
+    pairs = T * (T + 1) / 2
+    us = timed(lambda i: ops.masked_attention(qq, kv[i % 4, 0], kv[i % 4, 1], meta, H, KV, D, V, 0.7, blk, None, True), it)
+    line("attention in blocks, sink (split weights)", f"prompt T={T} heads={H}/{KV} D={D} block={blk}", us, 2.0 * H * (D + V) * pairs_blk, "bf16")
+    ops.fast_attention = False
+    us = timed(lambda i: ops.masked_attention(qq, kv[i % 4, 0], kv[i % 4, 1], meta, H, KV, D, V, 0.7, blk, None, True), 3)
+    line("attention in blocks, sink (float32 kernel)", f"prompt T={T} heads={H}/{KV} D={D} block={blk}", us, 2.0 * H * (D + V) * pairs_blk, "fma")
+    ops.fast_attention = True
+    meta.table_rows = None
+    us = timed(lambda i: ops.paged_attention(qq, kv[i % 4, 0], kv[i % 4, 1], meta, H, KV, 128, 0.1, None), it)
+    line("  Qwen3: attention", f"prompt T={T} heads={H}/{KV} D=128", us, 4.0 * H * 128 * pairs, "bf16")
+    p3 = torch.randn(4, T, (H + 2 * KV) * D, device="cuda", dtype=bf)
+    lam = torch.tensor([0.3], device="cuda")
+    us = timed(lambda i: ops.unit_qk_cache(p3[i % 4], H, KV, D, V, 1e-6, lam, p3[(i + 1) % 4][:, (H + KV) * D:], meta, kv[i % 4, 0], kv[i % 4, 1]), it)
+    line("unit norms, value blend, cache write", f"T={T} heads={H}/{KV}", us, T * ((H + 2 * KV) * D * 2.0 * 2 + KV * V * 2.0), "hbm")
+    nw, invf = torch.ones(D, device="cuda", dtype=bf), torch.full((D // 2,), 0.01, device="cuda")
+    us = timed(lambda i: ops.qk_norm_rope_cache(p3[i % 4], H, KV, D, nw, nw, 1e-6, invf, meta, kv[i % 4, 0], kv[i % 4, 1]), it)
+    line("  Qwen3: q/k norm, rotation, cache write", f"T={T} heads={H}/{KV}", us, T * (H + 2 * KV) * D * 2.0 * 2, "hbm")
+    ctx = args.ctx
+    pages = -(-ctx // ps)
+    for B in (8, 64):
+        layers = max(2, (512 << 20) // (B * pages * ps * KV * D * 4) + 1)
+        table = (torch.stack([torch.randperm(pages, device="cuda") for _ in range(B)]) + 1 + (torch.arange(B, device="cuda") * pages)[:, None]).to(torch.int32)
+        ar = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+        meta = types.SimpleNamespace(page_size=ps, tile=64, block_table=table.contiguous(), table_rows=ar[:B].contiguous(), max_pages=pages, seg_q_start=ar,
+                                     seg_pos0=torch.full((B,), ctx - 1, dtype=torch.int32, device="cuda"),
+                                     seg_kv_len=torch.full((B,), ctx, dtype=torch.int32, device="cuda"), decode_segs=ar[:B].contiguous(),
+                                     prefill_tiles=torch.zeros((0, 2), dtype=torch.int32, device="cuda"), prefill_tiles2=None, max_kv_len=ctx, num_tokens=B)
+        kv = torch.randn(layers, 2, B * pages + 1, KV, ps, D, device="cuda", dtype=bf)
+        qq = torch.randn(B, H * D, device="cuda", dtype=bf)
+        seen = (ctx - 1) % blk + 1
+        us = timed(lambda i: ops.masked_attention(qq, kv[i % layers, 0], kv[i % layers, 1], meta, H, KV, D, V, 0.7, blk, None, True), it)
+        line("attention in blocks, sink", f"decode B={B} ctx={ctx} sees {seen} heads={H}/{KV}", us, B * seen * KV * (D + V) * 2.0, "hbm")
+        meta.table_rows = None
+        us = timed(lambda i: ops.paged_attention(qq, kv[i % layers, 0], kv[i % layers, 1], meta, H, KV, 128, 0.1, None), it)
+        line("  Qwen3: attention", f"decode B={B} ctx={ctx} heads={H}/{KV} D=128", us, B * ctx * KV * 128 * 4.0, "hbm")
+        del kv
+    ops.check_errors()
+    return rows
+
+
+DESIGNS = {"naditar": (naditar_config, qwen3_config_like, bench_design), "namesun": (namesun_config, qwen3_config_like_namesun, bench_namesun)}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("what", choices=["gemm", "attention", "prefill", "design"])
+    ap.add_argument("what", choices=["gemm", "attention", "prefill", "design", "namesun"])
     ap.add_argument("--design-size", default="2k", choices=sorted(NADITAR_SIZES), help="design: layer sizes of the Naditar kernels")
     ap.add_argument("--size", default="4b", choices=sorted(SIZES))
     ap.add_argument("--rows", default="1,8,64", type=lambda s: [int(v) for v in s.split(",")])
@@ -339,7 +500,7 @@ def main(argv=None):
     ops = get_ops("cuda:0")
     peak, src = peak_gbs()
     print(f"# peak {peak} GB/s ({src})")
-    {"gemm": bench_gemm, "attention": bench_attention, "prefill": bench_prefill_attention, "design": bench_design}[args.what](args, ops, peak)
+    {"gemm": bench_gemm, "attention": bench_attention, "prefill": bench_prefill_attention, "design": bench_design, "namesun": bench_namesun}[args.what](args, ops, peak)
     return 0
 
 

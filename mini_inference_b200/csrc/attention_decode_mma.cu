@@ -87,7 +87,10 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
                        const int* __restrict__ seg_q_start, const int* __restrict__ seg_kv_len,
                        const int* __restrict__ block_table, const int* __restrict__ table_rows, int table_stride,
                        int H, int KV, int ps, float scale_log2, int window, int* __restrict__ merge_counters,
-                       int* __restrict__ error_word, int cluster_merge) {
+                       int* __restrict__ error_word, int cluster_merge, int block, int sink) {
+    // block > 0: the query (position len - 1) sees only the keys of its own block of positions, from floor((len - 1) / block) * block on.
+    // sink != 0: the softmax has one more term of score 0 that carries no value; ONE warp of ONE split starts its running maximum
+    // at 0 and its running sum at 1, and the merges of warps and of splits carry the term along like any other.
     static_assert(WARPS * DEC_STAGES * 8 <= DEC_BAR_BYTES, "the mbarriers must fit in their reserved bytes");
     constexpr int KS = D / 16;          // k-steps of the score product
     constexpr int NT = D / 8;           // output tiles of 8 columns
@@ -102,7 +105,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     const int seg = decode_segs[blockIdx.x], kvh = blockIdx.y;
     const int S = gridDim.z, s = blockIdx.z;
     const int tok = seg_q_start[seg], len = seg_kv_len[seg];
-    const int lo = window > 0 ? max(0, len - window) : 0;
+    const int lo = max(window > 0 ? max(0, len - window) : 0, block > 0 ? (len - 1) / block * block : 0);
     const int blk_lo = lo / 16, blk_hi = (len + 15) / 16;
     const int per = (blk_hi - blk_lo + S - 1) / S;
     const int b0 = blk_lo + s * per, b1 = min(b0 + per, blk_hi);
@@ -172,7 +175,8 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     float o[NT][4];
 #pragma unroll
     for (int t = 0; t < NT; ++t) { o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f; }
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // rows g and g + 8; sums are per thread
+    const bool has_sink = sink && s == 0 && warp == 0;
+    float m0 = has_sink ? 0.f : -INFINITY, m1 = m0, l0 = has_sink && c == 0 ? 1.f : 0.f, l1 = l0;      // rows g and g + 8; sums are per thread
 
     uint4 kreg[2][KS / 2];
     uint4 vreg[4][HALVES];
@@ -529,7 +533,7 @@ static int decode_mma_rows_launch(const void* q, int q_stride, const void* k_cac
                                   const int* seg_q_start, const int* seg_kv_len, const int* block_table,
                                   const int* table_rows, int table_stride, int H, int KV, int D, int ps, int splits,
                                   float scale, int window, int* merge_counters, int* error_word, int cache_pages,
-                                  int cluster_merge, cudaStream_t stream) {
+                                  int cluster_merge, cudaStream_t stream, int block = 0, int sink = 0) {
     if (num_decode == 0) return 0;
     if ((D != 64 && D != 128) || H % KV || H / KV > 16 || ps % 16 || q_stride % 8) return -2;
     dim3 grid(num_decode, KV, splits);
@@ -586,7 +590,7 @@ static int decode_mma_rows_launch(const void* q, int q_stride, const void* k_cac
         return (int)cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<DD, BB, WW, SPLIT>, kmap, vmap, \
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
             (__nv_bfloat16*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, block_table, table_rows, \
-            table_stride, H, KV, ps, scale_log2, window, merge_counters, error_word, use_cluster); } while (0)
+            table_stride, H, KV, ps, scale_log2, window, merge_counters, error_word, use_cluster, block, sink); } while (0)
     if (D == 128) { if (alone) LAUNCH(128, true, DEC_WARPS_ALONE); else if (bulk) LAUNCH(128, true, DEC_WARPS); else LAUNCH(128, false, DEC_WARPS); }
     else { if (alone) LAUNCH(64, true, DEC_WARPS_ALONE); else if (bulk) LAUNCH(64, true, DEC_WARPS); else LAUNCH(64, false, DEC_WARPS); }
 #undef LAUNCH
@@ -612,5 +616,15 @@ MI_EXPORT int mi_attn_decode_mma_rows_split(const void* q, int q_stride, const v
                                             float scale, int window, int* merge_counters, int* error_word, int cache_pages,
                                             int cluster_merge, cudaStream_t stream) {
     return decode_mma_rows_launch<true>(DECODE_ROWS_ARGS);
+}
+
+// Split weights, and the mask and softmax of csrc/attention_masked.cu: blocks of positions (block > 0), a sink term (sink != 0).
+MI_EXPORT int mi_attn_decode_mma_rows_masked(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                             float* o_part, float* lse_part, const int* decode_segs, int num_decode,
+                                             const int* seg_q_start, const int* seg_kv_len, const int* block_table,
+                                             const int* table_rows, int table_stride, int H, int KV, int D, int ps, int splits,
+                                             float scale, int window, int* merge_counters, int* error_word, int cache_pages,
+                                             int cluster_merge, int block, int sink, cudaStream_t stream) {
+    return decode_mma_rows_launch<true>(DECODE_ROWS_ARGS, block, sink);
 }
 #undef DECODE_ROWS_ARGS
