@@ -389,12 +389,12 @@ def bench_namesun(args, ops, peak, out=print):
     # ---- routed experts beside the dense feed-forward of equal active size
     for rows_n in (T, 64, 8):
         h = torch.randn(rows_n, W, device="cuda", dtype=bf)
-        router, corr = torch.randn(E, W, device="cuda") * 0.05, torch.zeros(E, device="cuda")
+        router, corr = (torch.randn(E, W, device="cuda") * 0.05).to(bf), torch.zeros(E, device="cuda")
         reps = 4 if rows_n > 64 else max(2, (300 << 20) // (E * 3 * F * W * 2) + 1)
         w_in = torch.randn(reps, E, 2 * F, W, device="cuda", dtype=bf) * 0.02
         w_out = torch.randn(reps, E, W, F, device="cuda", dtype=bf) * 0.02
         us = timed(lambda i: ops.route_topk(h, router, corr, top, z["groups"]), it)
-        line("router: logits, softmax, grouped top-k", f"rows={rows_n} experts={E} top={top}", us, rows_n * W * 2.0 + E * W * 4.0, "hbm")
+        line("router: logits, softmax, grouped top-k", f"rows={rows_n} experts={E} top={top}", us, rows_n * W * 2.0 + E * W * 2.0, "hbm")
         chosen, wts = ops.route_topk(h, router, corr, top, z["groups"])
         us = timed(lambda i: ops.expert_ffn(h, chosen, wts, w_in[i % reps], w_out[i % reps], 7.0, 1.702, None), it)
         flops = 2.0 * rows_n * top * 3 * F * W

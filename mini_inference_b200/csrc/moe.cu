@@ -19,6 +19,7 @@
 // float32 form on the CUDA cores (true 32-bit, sums in a fixed order along K) that also takes bfloat16 shapes the first
 // does not.
 #include "common.cuh"
+#include <limits.h>
 #include <math.h>
 
 using namespace mi;
@@ -26,59 +27,115 @@ using namespace mi;
 namespace {
 
 // ------------------------------------------------------------------ router
-template <typename T>
-__global__ void route_topk_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ router, const float* __restrict__ corr,
-                                  int* __restrict__ chosen, float* __restrict__ weights, int hidden, int E, int top, int g_count,
-                                  int g_keep) {
-    extern __shared__ float rsm[];
-    float* hs = rsm;                       // [hidden]
-    float* s = hs + hidden;                // [E] logits, then softmax scores
-    float* c = s + E;                      // [E] choice scores
-    float* gb = c + E;                     // [E] best choice score per group / kept flags
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    const T* row = h + (size_t)t * ldh;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) hs[i] = to_f32(row[i]);
-    __syncthreads();
-    for (int e = warp; e < E; e += nw) {
-        const float* w = router + (size_t)e * hidden;
-        float dot = 0.f;
-        for (int i = lane; i < hidden; i += 32) dot = fmaf(hs[i], w[i], dot);
-        dot = warp_sum(dot);
-        if (lane == 0) s[e] = dot;
+// (value, index) of the best candidate over a warp: the larger value, on a tie the lower index; index INT_MAX: none
+__device__ __forceinline__ void warp_best(float& bv, int& bi) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi != INT_MAX && (bi == INT_MAX || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
     }
-    __syncthreads();
-    if (threadIdx.x != 0) return;
+}
+
+// One warp makes one token's choice from its logits s[E] (left as softmax scores); c and gb are scratch of E floats each.
+__device__ __forceinline__ void warp_choose(float* s, float* c, float* gb, const float* __restrict__ corr, int E, int top, int g_count,
+                                            int g_keep, int* __restrict__ chosen, float* __restrict__ weights, int lane) {
     float mx = -INFINITY, den = 0.f;
-    for (int e = 0; e < E; ++e) mx = fmaxf(mx, s[e]);
-    for (int e = 0; e < E; ++e) { s[e] = expf(s[e] - mx); den += s[e]; }
-    for (int e = 0; e < E; ++e) { s[e] = s[e] / den; c[e] = s[e] + corr[e]; }
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
+    mx = warp_max(mx);
+    for (int e = lane; e < E; e += 32) { const float v = expf(s[e] - mx); s[e] = v; den += v; }
+    den = warp_sum(den);
+    for (int e = lane; e < E; e += 32) { s[e] = s[e] / den; c[e] = s[e] + corr[e]; }
+    __syncwarp();
     if (g_count > 0) {
         const int per = E / g_count;
-        for (int g = 0; g < g_count; ++g) {
+        for (int g = lane; g < g_count; g += 32) {
             float b = -INFINITY;
             for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, c[e]);
             gb[g] = b;
         }
-        // the g_keep best groups: their entry becomes +inf (kept), every other one ends as -inf
-        for (int k = 0; k < g_keep; ++k) {
-            int best = -1;
+        __syncwarp();
+        for (int k = 0; k < g_keep; ++k) {                 // a kept group's entry becomes +inf
             float bv = -INFINITY;
-            for (int g = 0; g < g_count; ++g)
-                if (gb[g] != INFINITY && (best < 0 || gb[g] > bv)) { best = g; bv = gb[g]; }
-            if (best >= 0) gb[best] = INFINITY;
+            int bi = INT_MAX;
+            for (int g = lane; g < g_count; g += 32)
+                if (gb[g] != INFINITY && (bi == INT_MAX || gb[g] > bv)) { bv = gb[g]; bi = g; }
+            warp_best(bv, bi);
+            __syncwarp();
+            if (lane == 0 && bi != INT_MAX) gb[bi] = INFINITY;
+            __syncwarp();
         }
-        for (int e = 0; e < E; ++e)
+        for (int e = lane; e < E; e += 32)
             if (gb[e / per] != INFINITY) c[e] = -INFINITY;
+        __syncwarp();
     }
     for (int j = 0; j < top; ++j) {
-        int best = -1;
         float bv = -INFINITY;
-        for (int e = 0; e < E; ++e)
-            if (!isnan(c[e]) && (best < 0 ? c[e] > -INFINITY : c[e] > bv)) { best = e; bv = c[e]; }
-        if (best < 0) best = 0;            // fewer eligible experts than `top`: the configuration reader refuses that
-        chosen[(size_t)t * top + j] = best;
-        weights[(size_t)t * top + j] = s[best];
-        c[best] = NAN;                     // taken
+        int bi = INT_MAX;
+        for (int e = lane; e < E; e += 32)
+            if (!isnan(c[e]) && c[e] > -INFINITY && (bi == INT_MAX || c[e] > bv)) { bv = c[e]; bi = e; }
+        warp_best(bv, bi);
+        if (bi == INT_MAX) bi = 0;         // fewer eligible experts than `top`: the configuration reader refuses that
+        __syncwarp();
+        if (lane == 0) { chosen[j] = bi; weights[j] = s[bi]; c[bi] = NAN; }       // NaN: taken
+        __syncwarp();
+    }
+}
+
+// One block of 8 warps per TOK tokens.  The tokens' rows wait in shared memory as float32; a warp takes experts in turn and
+// reads an expert's router row ONCE for all TOK tokens (with one token per block every token would fetch the whole matrix
+// again).  Sums are float32, per lane in steps of the row, then across the lanes in a fixed order, so a token's logits do
+// not depend on its neighbours.  Warp i of the block then makes token i's choice.
+template <typename T, int TOK>
+__global__ void __launch_bounds__(256) route_topk_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ router, const float* __restrict__ corr,
+                                                         int* __restrict__ chosen, float* __restrict__ weights, int T_, int hidden, int E, int top,
+                                                         int g_count, int g_keep) {
+    extern __shared__ __align__(16) float rsm[];
+    float* hs = rsm;                                   // [TOK][hidden]
+    float* sc = hs + (size_t)TOK * hidden;             // [TOK][3][E]: scores, choice scores, group scratch
+    const int t0 = blockIdx.x * TOK, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int nt = min(TOK, T_ - t0);
+    for (int i = threadIdx.x; i < TOK * hidden; i += blockDim.x) {
+        const int tk = i / hidden, c = i % hidden;
+        hs[i] = tk < nt ? to_f32(h[(size_t)(t0 + tk) * ldh + c]) : 0.f;
+    }
+    __syncthreads();
+    const bool vec = hidden % 4 == 0 && ((uintptr_t)router % 16) == 0;
+    for (int e = warp; e < E; e += nw) {
+        const T* w = router + (size_t)e * hidden;
+        float dot[TOK];
+#pragma unroll
+        for (int k = 0; k < TOK; ++k) dot[k] = 0.f;
+        if (vec) {                                     // four neighbouring entries per lane and step: the lanes of a warp read one
+            for (int i = lane * 4; i < hidden; i += 128) {         // contiguous piece of the row and of every token (no bank conflicts)
+                float w0, w1, w2, w3;
+                load2(w + i, w0, w1);
+                load2(w + i + 2, w2, w3);
+#pragma unroll
+                for (int k = 0; k < TOK; ++k) {
+                    const float4 hv = *reinterpret_cast<const float4*>(hs + (size_t)k * hidden + i);
+                    dot[k] = fmaf(hv.x, w0, dot[k]); dot[k] = fmaf(hv.y, w1, dot[k]);
+                    dot[k] = fmaf(hv.z, w2, dot[k]); dot[k] = fmaf(hv.w, w3, dot[k]);
+                }
+            }
+        } else {
+            for (int i = lane; i < hidden; i += 32) {
+                const float wv = to_f32(w[i]);
+#pragma unroll
+                for (int k = 0; k < TOK; ++k) dot[k] = fmaf(hs[(size_t)k * hidden + i], wv, dot[k]);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < TOK; ++k) {
+            const float d = warp_sum(dot[k]);
+            if (lane == 0) sc[(size_t)k * 3 * E + e] = d;
+        }
+    }
+    __syncthreads();
+    for (int tk = warp; tk < nt; tk += nw) {
+        float* s = sc + (size_t)tk * 3 * E;
+        const size_t t = t0 + tk;
+        warp_choose(s, s + E, s + 2 * E, corr, E, top, g_count, g_keep, chosen + t * top, weights + t * top, lane);
     }
 }
 
@@ -90,9 +147,22 @@ __device__ __forceinline__ float clamped_glu(float g, float u, float limit, floa
 }
 
 template <typename T>
-__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, float limit, float slope) {
+__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, float limit, float slope, int vec) {
     const T* row = gu + (size_t)blockIdx.x * 2 * inter;
     T* o = out + (size_t)blockIdx.x * inter;
+    constexpr int VN = Vec16<T>::N;
+    if (vec) {                                                      // 16 bytes of gate and of up per thread and step
+        for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * VN; i < inter; i += gridDim.y * blockDim.x * VN) {
+            float g[VN], u[VN];
+            load16(row + i, g);
+            load16(row + inter + i, u);
+            T y[VN];
+#pragma unroll
+            for (int j = 0; j < VN; ++j) y[j] = from_f32<T>(clamped_glu(g[j], u[j], limit, slope));
+            *reinterpret_cast<uint4*>(o + i) = *reinterpret_cast<const uint4*>(y);
+        }
+        return;
+    }
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x)
         o[i] = from_f32<T>(clamped_glu(to_f32(row[i]), to_f32(row[inter + i]), limit, slope));
 }
@@ -194,8 +264,8 @@ __global__ void __launch_bounds__(256) moe_gemm_simt_kernel(const T* __restrict_
 // ------------------------------------------------------------------ grouped product, bfloat16 on mma.sync tiles
 // A block of 8 warps (WM x WN) owns BM = 16 MT WM sorted rows of ONE expert and 128 rows of the expert's matrix
 // (MODE 1: 128 output columns; MODE 0: 64 gate rows and the 64 up rows of the same columns, interleaved per warp so that
-// a thread holds gate and up of the same output in its accumulators).  K runs in steps of 32 through a three-stage
-// cp.async ring; rows of shared memory are padded to 80 bytes, which keeps ldmatrix free of bank conflicts.
+// a thread holds gate and up of the same output in its accumulators).  K runs in steps of 64 through a three-stage
+// cp.async ring; rows of shared memory are padded to 144 bytes, which keeps ldmatrix free of bank conflicts.
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -210,10 +280,10 @@ __device__ __forceinline__ void cp16(uint32_t dst, const void* src, bool valid) 
 __device__ __forceinline__ void cp_commit_group() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_wait_group() { asm volatile("cp.async.wait_group %0;\n" :: "n"(N) : "memory"); }
 
-constexpr int TK = 32, TROW = 40, TSTAGES = 3;                      // k per stage, padded row (elements), ring depth
+constexpr int TK = 64, TROW = 72, TSTAGES = 3;                      // k per stage, padded row (elements), ring depth
 
 template <int MODE, int MT, int WM, int WN>
-__global__ void __launch_bounds__(256) moe_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W,
+__global__ void __launch_bounds__(256, 2) moe_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W,
                                                           __nv_bfloat16* __restrict__ out, int ldo, const int* __restrict__ sorted_pair,
                                                           const int* __restrict__ tile_expert, int top, int N, int K, float limit, float slope) {
     constexpr int BM = 16 * MT * WM, WNE = 128 / WN, NT = WNE / 8, BN_OUT = MODE == 0 ? 64 : 128;
@@ -229,15 +299,16 @@ __global__ void __launch_bounds__(256) moe_gemm_tc_kernel(const __nv_bfloat16* _
     __syncthreads();
     const __nv_bfloat16* We = W + (size_t)e * (MODE == 0 ? 2 : 1) * N * K;
     // what this thread copies per stage: chunks of 16 bytes, (row, k chunk)
-    constexpr int A_CH = BM * 4, B_CH = 128 * 4;
+    constexpr int CPR = TK / 8;                                     // 16-byte chunks per row and stage
+    constexpr int A_CH = BM * CPR, B_CH = 128 * CPR;
     auto load_stage = [&](int stage, int k0) {
         for (int c = tid; c < A_CH; c += 256) {
-            const int r = c >> 2, kc = c & 3, pr = pair_s[r];
+            const int r = c / CPR, kc = c % CPR, pr = pair_s[r];
             const long long src = MODE == 0 ? pr / top : pos0 + r;
             cp16((uint32_t)__cvta_generic_to_shared(sA + (stage * BM + r) * TROW + kc * 8), A + (pr >= 0 ? src * lda + k0 + kc * 8 : 0), pr >= 0);
         }
         for (int c = tid; c < B_CH; c += 256) {
-            const int r = c >> 2, kc = c & 3;
+            const int r = c / CPR, kc = c % CPR;
             int col, grow;
             if (MODE == 0) {                                        // warp w's rows: its gate columns, then the up rows of the same columns
                 const int w = r / WNE, rr = r % WNE;
@@ -330,26 +401,33 @@ __global__ void moe_combine_kernel(const T* __restrict__ rows, const float* __re
 
 }  // namespace
 
-MI_EXPORT int mi_route_topk(const void* h, int ldh, const float* router, const float* corr, int* chosen, float* weights, int T_, int hidden,
+// router [E, hidden] in the dtype of h (its values are read as they are stored and multiplied and added in float32)
+MI_EXPORT int mi_route_topk(const void* h, int ldh, const void* router, const float* corr, int* chosen, float* weights, int T_, int hidden,
                             int E, int top, int g_count, int g_keep, int dtype, cudaStream_t stream) {
     if (T_ == 0) return 0;
-    const size_t smem = ((size_t)hidden + 3 * (size_t)E) * sizeof(float);
-    if (smem > 200 * 1024 || top > E || (g_count > 0 && E % g_count)) return -2;
-    if (dtype == MI_BF16) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(route_topk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        route_topk_kernel<__nv_bfloat16><<<T_, 128, smem, stream>>>((const __nv_bfloat16*)h, ldh, router, corr, chosen, weights, hidden, E, top, g_count, g_keep);
-    } else {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(route_topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        route_topk_kernel<float><<<T_, 128, smem, stream>>>((const float*)h, ldh, router, corr, chosen, weights, hidden, E, top, g_count, g_keep);
-    }
+    if (top > E || (g_count > 0 && E % g_count)) return -2;
+    const int tok = T_ >= 1024 ? 8 : 1;
+    const size_t smem = ((size_t)tok * hidden + 3 * (size_t)tok * E) * sizeof(float);
+    if (smem > 200 * 1024) return -2;
+    const int grid = (T_ + tok - 1) / tok;
+#define GO(T, TOK) do { \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(route_topk_kernel<T, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        route_topk_kernel<T, TOK><<<grid, 256, smem, stream>>>((const T*)h, ldh, (const T*)router, corr, chosen, weights, T_, hidden, E, top, \
+                                                               g_count, g_keep); } while (0)
+    if (dtype == MI_BF16) { if (tok == 8) GO(__nv_bfloat16, 8); else GO(__nv_bfloat16, 1); }
+    else { if (tok == 8) GO(float, 8); else GO(float, 1); }
+#undef GO
     return (int)cudaGetLastError();
 }
 
 MI_EXPORT int mi_clamped_glu(const void* gu, void* out, int rows, int inter, float limit, float slope, int dtype, cudaStream_t stream) {
     if (rows == 0) return 0;
-    dim3 grid(rows, rows >= 512 ? 1 : min(16, (inter + 255) / 256));
-    if (dtype == MI_BF16) clamped_glu_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, limit, slope);
-    else clamped_glu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, inter, limit, slope);
+    const int vn = dtype == MI_BF16 ? 8 : 4;
+    const int vec = inter % vn == 0 && ((uintptr_t)gu % 16) == 0 && ((uintptr_t)out % 16) == 0;
+    const int per = vec ? 256 * vn : 256;
+    dim3 grid(rows, rows >= 512 ? 1 : min(16, (inter + per - 1) / per));
+    if (dtype == MI_BF16) clamped_glu_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, limit, slope, vec);
+    else clamped_glu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, inter, limit, slope, vec);
     return (int)cudaGetLastError();
 }
 
@@ -384,7 +462,7 @@ MI_EXPORT int mi_moe_tile_rows_tc(int P, int E) {
     return avg > 48 ? 128 : avg > 12 ? 64 : 16;
 }
 
-// bfloat16 only; K % 32 == 0, N even, lda % 8 == 0; BM as mi_moe_tile_rows_tc said (and as mi_moe_align sorted)
+// bfloat16 only; K % 64 == 0, N even, lda % 8 == 0; BM as mi_moe_tile_rows_tc said (and as mi_moe_align sorted)
 MI_EXPORT int mi_moe_gemm_tc(const void* A, int lda, const void* W, void* out, int ldo, const int* sorted_pair, const int* tile_expert,
                              int cap_tiles, int top, int N, int K, float limit, float slope, int mode, int BM, int dtype, cudaStream_t stream) {
     if (cap_tiles == 0) return 0;

@@ -131,6 +131,8 @@ class CudaOps:
         self.latent_tc = os.environ.get("MI_LATENT_TC", "0") == "1"
         # the grouped products of routed experts on mma.sync tensor-core tiles (bfloat16); MI_MOE_TC=0: the CUDA-core form
         self.moe_tc = os.environ.get("MI_MOE_TC", "1") == "1" and hasattr(self.lib, "mi_moe_gemm_tc")
+        # ... and, where an expert gets many rows, on tcgen05 tiles of 128 sorted rows (csrc/moe_grouped_tc.cu); MI_MOE_TCGEN05=0: never
+        self.moe_tcgen05 = os.environ.get("MI_MOE_TCGEN05", "1") == "1"
         self.launches = 0                    # kernels of this package launched so far
 
     def _stream(self):
@@ -468,7 +470,7 @@ class CudaOps:
         if code != 0:
             self._stream_error.zero_()
             self._tc2_counters.zero_()
-            raise RuntimeError(f"a pipeline wait inside a kernel ran out (code {code}: 1-2 gemm_stream, 21+ attention, 51-55 gemm_tc2)")
+            raise RuntimeError(f"a pipeline wait inside a kernel ran out (code {code}: 1-2 gemm_stream, 21+ attention, 51-55 gemm_tc2, 61-63 grouped expert product)")
 
     # ---------------------------------------------------------------- q/k norm, rotation, cache write
     def qk_norm_rope_cache(self, qkv, H, KV, D, q_weight, k_weight, eps, inv_freq, meta, k_cache, v_cache):
@@ -906,10 +908,10 @@ class CudaOps:
 
     # ---------------------------------------------------------------- routed experts
     def route_topk(self, h, router, correction, top, groups):
-        """(chosen int32 [T, top], weights float32 [T, top]).  router float32 [E, hidden], correction float32 [E]; groups None or
-        (count, keep).  Logits, softmax and the choice are float32 (csrc/moe.cu)."""
+        """(chosen int32 [T, top], weights float32 [T, top]).  router [E, hidden] in the dtype of h, correction float32 [E];
+        groups None or (count, keep).  Products, sums, softmax and the choice are float32 (csrc/moe.cu)."""
         T, E = h.shape[0], router.shape[0]
-        assert h.stride(1) == 1 and router.dtype == torch.float32 and router.is_contiguous() and correction.dtype == torch.float32
+        assert h.stride(1) == 1 and router.dtype == h.dtype and router.is_contiguous() and correction.dtype == torch.float32
         chosen = torch.empty((T, top), dtype=torch.int32, device=h.device)
         weights = torch.empty((T, top), dtype=torch.float32, device=h.device)
         count, keep = groups if groups else (0, 0)
@@ -937,7 +939,28 @@ class CudaOps:
         F, hidden = F2 // 2, w_out.shape[1]
         assert h.stride(1) == 1 and w_in.is_contiguous() and w_out.is_contiguous() and K == h.shape[1] and w_in.dtype == h.dtype
         P, code, dev = T * top, _code(h.dtype), h.device
-        tc = h.dtype == torch.bfloat16 and self.moe_tc and K % 32 == 0 and F % 32 == 0 and h.stride(0) % 8 == 0
+        if (h.dtype == torch.bfloat16 and self.moe_tcgen05 and P > 48 * E and K % 64 == 0 and F % 64 == 0 and hidden % 8 == 0
+                and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0):
+            # many rows per expert: tiles of 128 sorted rows on the tcgen05 tensor cores (csrc/moe_grouped_tc.cu)
+            cap_tiles = (P + 127) // 128 + min(E, P)
+            cap_pos = cap_tiles * 128
+            sorted_pair = torch.empty(cap_pos, dtype=torch.int32, device=dev)
+            tile_expert = torch.empty(cap_tiles, dtype=torch.int32, device=dev)
+            _check(self.lib.mi_moe_align(_p(chosen), P, E, 128, _p(sorted_pair), cap_pos, _p(tile_expert), cap_tiles, self._stream()), "moe_align")
+            a = torch.empty((cap_pos, K), dtype=h.dtype, device=dev)
+            _check(self.lib.mi_moe_gather_rows(_p(h), h.stride(0), _p(sorted_pair), top, _p(a), cap_pos, K, self._stream()), "moe_gather_rows")
+            y = torch.empty((cap_pos, F), dtype=h.dtype, device=dev)
+            rows = torch.empty((P, hidden), dtype=h.dtype, device=dev)
+            _check(self.lib.mi_moe_gemm_tcgen05(_p(a), _p(w_in), E, _p(y), F, _p(sorted_pair), _p(tile_expert), cap_tiles, F, K,
+                                                _c.c_float(limit), _c.c_float(slope), 0, _p(self._stream_error), self._stream()), "moe_gemm_tcgen05 (in)")
+            _check(self.lib.mi_moe_gemm_tcgen05(_p(y), _p(w_out), E, _p(rows), hidden, _p(sorted_pair), _p(tile_expert), cap_tiles, hidden, F,
+                                                _c.c_float(limit), _c.c_float(slope), 1, _p(self._stream_error), self._stream()), "moe_gemm_tcgen05 (out)")
+            out = torch.empty((T, hidden), dtype=h.dtype, device=dev)
+            assert shared is None or (shared.is_contiguous() and shared.shape == out.shape)
+            _check(self.lib.mi_moe_combine(_p(rows), _p(weights), _p(shared), _p(out), T, hidden, top, code, self._stream()), "moe_combine")
+            self.launches += 5
+            return out
+        tc = h.dtype == torch.bfloat16 and self.moe_tc and K % 64 == 0 and F % 64 == 0 and hidden % 2 == 0 and h.stride(0) % 8 == 0
         BM = int(self.lib.mi_moe_tile_rows_tc(P, E) if tc else self.lib.mi_moe_tile_rows_simt())
         cap_tiles = (P + BM - 1) // BM + min(E, P)
         cap_pos = cap_tiles * BM

@@ -114,7 +114,7 @@ class RoutedExperts(Part):
         return specs
 
     def load(self, tensors, dtype, device):
-        self.router = tensors.pop("router").float().contiguous()           # the router's logits are float32 sums
+        self.router = tensors.pop("router").contiguous()                   # stored values as they are; products and sums are float32
         self.correction = tensors.pop("correction").float().contiguous()
         # per expert [gate rows | up rows] and the down matrix, stacked: one grouped product each
         self.w_in = torch.stack([torch.cat([tensors.pop(f"e{e}.gate"), tensors.pop(f"e{e}.up")], dim=0) for e in range(self.E)]).contiguous()

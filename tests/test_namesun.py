@@ -663,20 +663,22 @@ def test_kernels_against_the_stand_ins(dtype):
         assert close(oa, ref.retention_scan(p, H, D, V, inv, D ** -0.5, decay, sb, batch), 1e-4 if dtype == torch.float32 else tol)
         assert close(sa, sb, 1e-4)
     # router and experts
-    for T, hid, E, top, groups, F in ((13, 44, 6, 2, (3, 2), 10), (70, 96, 16, 5, (4, 2), 32), (5, 33, 7, 7, None, 9), (40, 64, 8, 1, (8, 1), 64),
-                                      (300, 64, 4, 2, None, 96)):
-        h, router, corr = rnd(T, hid), f32(E, hid) * 0.5, f32(E) * 0.2
+    for T, hid, E, top, groups, F in ((13, 44, 6, 2, (3, 2), 10), (70, 128, 16, 5, (4, 2), 64), (5, 33, 7, 7, None, 9), (40, 64, 8, 1, (8, 1), 64),
+                                      (300, 64, 4, 2, None, 192), (1100, 72, 6, 2, (3, 2), 8), (900, 320, 5, 3, None, 448)):
+        h, router, corr = rnd(T, hid), rnd(E, hid) * 0.5, f32(E) * 0.2
         ca, wa = ops.route_topk(h.to(dev), router.to(dev), corr.to(dev), top, groups)
         cb, wb = ref.route_topk(h, router, corr, top, groups)
         assert torch.equal(ca.cpu(), cb) and close(wa, wb, 1e-5)
         w_in, w_out, shared = rnd(E, 2 * F, hid) * 0.3, rnd(E, hid, F) * 0.3, rnd(T, hid)
         for sh in (None, shared):
-            for tc in ((False, True) if dtype == torch.bfloat16 else (False,)):
-                ops.moe_tc, keep = tc and ops.moe_tc, ops.moe_tc
+            # bfloat16: the CUDA-core form, the mma.sync form, and (where an expert gets many rows) the tcgen05 form
+            for tc, tc5 in (((False, False), (True, False), (True, True)) if dtype == torch.bfloat16 else ((False, False),)):
+                keep = (ops.moe_tc, ops.moe_tcgen05)
+                ops.moe_tc, ops.moe_tcgen05 = tc and keep[0], tc5 and keep[1]
                 try:
                     got = ops.expert_ffn(h.to(dev), ca, wa, w_in.to(dev), w_out.to(dev), 1.3, 1.702, None if sh is None else sh.to(dev))
                 finally:
-                    ops.moe_tc = keep
+                    ops.moe_tc, ops.moe_tcgen05 = keep
                 assert close(got, ref.expert_ffn(h, cb, wb, w_in, w_out, 1.3, 1.702, sh))
         gu = rnd(T, 2 * F) * 3
         assert close(ops.clamped_glu(gu.to(dev), 1.3, 1.702), ref.clamped_glu(gu, 1.3, 1.702))
