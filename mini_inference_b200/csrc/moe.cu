@@ -107,6 +107,7 @@ __global__ void __launch_bounds__(256) route_topk_kernel(const T* __restrict__ h
 #pragma unroll
         for (int k = 0; k < TOK; ++k) dot[k] = 0.f;
         if (vec) {                                     // four neighbouring entries per lane and step: the lanes of a warp read one
+#pragma unroll 4
             for (int i = lane * 4; i < hidden; i += 128) {         // contiguous piece of the row and of every token (no bank conflicts)
                 float w0, w1, w2, w3;
                 load2(w + i, w0, w1);
