@@ -82,12 +82,13 @@ __device__ __forceinline__ void warp_choose(float* s, float* c, float* gb, const
     }
 }
 
-// One block of 8 warps per TOK tokens.  The tokens' rows wait in shared memory as float32; a warp takes experts in turn and
+// One block per TOK tokens: 8 warps for 8 tokens (prompt steps), up to a warp per expert for one token (decode steps, where the
+// time is the chain of loads of one warp).  The tokens' rows wait in shared memory as float32; a warp takes experts in turn and
 // reads an expert's router row ONCE for all TOK tokens (with one token per block every token would fetch the whole matrix
 // again).  Sums are float32, per lane in steps of the row, then across the lanes in a fixed order, so a token's logits do
 // not depend on its neighbours.  Warp i of the block then makes token i's choice.
 template <typename T, int TOK>
-__global__ void __launch_bounds__(256) route_topk_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ router, const float* __restrict__ corr,
+__global__ void __launch_bounds__(TOK == 1 ? 1024 : 256) route_topk_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ router, const float* __restrict__ corr,
                                                          int* __restrict__ chosen, float* __restrict__ weights, int T_, int hidden, int E, int top,
                                                          int g_count, int g_keep) {
     extern __shared__ __align__(16) float rsm[];
@@ -413,7 +414,7 @@ MI_EXPORT int mi_route_topk(const void* h, int ldh, const void* router, const fl
     const int grid = (T_ + tok - 1) / tok;
 #define GO(T, TOK) do { \
         if (smem > 48 * 1024) cudaFuncSetAttribute(route_topk_kernel<T, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        route_topk_kernel<T, TOK><<<grid, 256, smem, stream>>>((const T*)h, ldh, (const T*)router, corr, chosen, weights, T_, hidden, E, top, \
+        route_topk_kernel<T, TOK><<<grid, TOK == 1 ? min(1024, max(128, 32 * E)) : 256, smem, stream>>>((const T*)h, ldh, (const T*)router, corr, chosen, weights, T_, hidden, E, top, \
                                                                g_count, g_keep); } while (0)
     if (dtype == MI_BF16) { if (tok == 8) GO(__nv_bfloat16, 8); else GO(__nv_bfloat16, 1); }
     else { if (tok == 8) GO(float, 8); else GO(float, 1); }
