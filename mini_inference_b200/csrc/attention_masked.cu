@@ -4,7 +4,7 @@
 //             (blocks counted from position 0 of the sequence); with window > 0 only the last `window`
 //   sink      one more softmax term whose score is 0 and which carries no value: p_j = exp(s_j) / (1 + sum exp(s_j));
 //             a running maximum that starts at 0 with a running sum that starts at 1 is exactly that
-//   sizes     key rows of D and value rows of Dv entries (multiples of 8, up to 256), each in a pool of its own:
+//   sizes     key rows of D and value rows of Dv entries (up to 256; any size, 16-byte loads where rows allow), each in a pool of its own:
 //             k_cache [pages, KV, page_size, D], v_cache [pages, KV, page_size, Dv]
 //
 // All arithmetic is float32 on the CUDA cores (scores, softmax weights and the weighted sum), in an order that
@@ -39,10 +39,14 @@ __device__ __forceinline__ void attend_keys(const float* q_s, const T* __restric
             row = (long long)(table_row[j / ps] * KV + kvh) * ps + j % ps;
             const T* kr = k_cache + row * D;
             float dot = 0.f, tmp[VN];
-            for (int c = 0; c < D; c += VN) {
-                load16(kr + c, tmp);
+            if (D % VN == 0) {                                     // rows start on 16 bytes: 16-byte loads
+                for (int c = 0; c < D; c += VN) {
+                    load16(kr + c, tmp);
 #pragma unroll
-                for (int e = 0; e < VN; ++e) dot += q_s[c + e] * tmp[e];
+                    for (int e = 0; e < VN; ++e) dot += q_s[c + e] * tmp[e];
+                }
+            } else {
+                for (int c = 0; c < D; ++c) dot += q_s[c] * to_f32(kr[c]);
             }
             s = dot;
         }
@@ -224,7 +228,7 @@ MI_EXPORT int mi_masked_prefill(const void* q, int q_stride, const void* k_cache
                                 const int* table_rows, int table_stride, int H, int KV, int D, int Dv, int ps, int tile_rows, float scale,
                                 int block, int window, int sink, int dtype, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
-    if (D > MAX_D || Dv > MAX_D || D % 8 || (dtype == MI_F32 && D % 4) || H > 65535) return -2;
+    if (D > MAX_D || Dv > MAX_D || H > 65535) return -2;
     dim3 grid(num_tiles, H);
 #define ARGS(T) (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, (T*)out, tiles, seg_q_start, seg_pos0, block_table, table_rows, \
         table_stride, H, KV, D, Dv, ps, tile_rows, scale, block, window, sink
@@ -239,7 +243,7 @@ MI_EXPORT int mi_masked_decode(const void* q, int q_stride, const void* k_cache,
                                const int* block_table, const int* table_rows, int table_stride, int H, int KV, int D, int Dv, int ps,
                                int splits, float scale, int block, int window, int sink, int dtype, cudaStream_t stream) {
     if (num_decode == 0) return 0;
-    if (D > MAX_D || Dv > MAX_D || D % 8 || H > 65535 * WARPS) return -2;
+    if (D > MAX_D || Dv > MAX_D || H > 65535 * WARPS) return -2;
     dim3 grid(num_decode, (H + WARPS - 1) / WARPS, splits);
 #define ARGS(T) (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, (T*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, \
         block_table, table_rows, table_stride, H, KV, D, Dv, ps, scale, block, window, sink

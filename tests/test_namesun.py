@@ -317,6 +317,7 @@ SINGLE = {
     "experts_plain": config(40, 71, [ret(1, 4, 4, [0.5], mlp=moe(5, 2, 11, 4.0))]),
     # sizes that put every view of a fused product on an odd offset
     "attention_odd": config(27, 53, [attn(3, 1, 8, 5, block=3)]),
+    "attention_odd_keys": config(27, 53, [attn(2, 2, 7, 3, block=6), attn(4, 1, 10, 9)]),
     # key and value rows of 64 entries: in bfloat16 on the GPU prompt portions take the tensor-core kernel
     "attention_rows64": config(48, 61, [attn(3, 1, 64, 64, block=40), attn(2, 2, 64, 64)]),
     "retention_odd": config(27, 53, [ret(3, 5, 7, [0.4, 0.8, 0.95], rot_dims=2)]),
