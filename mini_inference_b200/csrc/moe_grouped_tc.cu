@@ -3,9 +3,16 @@
 // The (token, choice) pairs have been sorted by expert, every expert's rows starting on a multiple of 128 (csrc/moe.cu,
 // moe_align), so a tile of 128 sorted rows belongs to ONE expert and both operands of its product are plain 2-D boxes:
 // rows [pos0, pos0 + 128) of the sorted activations and 256 rows of that expert's matrix.  One block per (row tile,
-// 256 accumulator columns): a TMA thread fills a four-stage ring (K in steps of 64, 128-byte swizzle), one thread issues
-// tcgen05.mma (M = 128, N = 256, accumulator in tensor memory), and the block's four warps read the accumulator back,
-// each its own 32 lanes, and write the result.
+// 256 accumulator columns), two blocks to an SM (two ring stages of 48 KB and 256 of the 512 tensor-memory columns each), so that one
+// block's start-up and epilogue run under the other's products: a TMA thread fills the ring (K in steps of 64, 128-byte swizzle), one thread issues
+// tcgen05.mma (M = 128, N = 256, accumulator in tensor memory), and the block's eight warps read the accumulator back
+// (a warp reaches the 32 lanes of its quarter; two warps share a quarter and take half of the columns each) and write the
+// result.  With four warps and the exact exponential and division the epilogue of a tile took longer than its products
+// (knock-out builds: the whole op 247 us; without loads 258; without loads and epilogue 125): a thread per row is a long
+// chain of dependent instructions with one warp per scheduler to hide it.  Hence eight warps and the fast exponential and
+// reciprocal, whose error (2^-21 relative) is far below the bfloat16 rounding of the result (212 us).  What is left is the
+// operands' way through shared memory: a block that feeds M = 128 / N = 256 products from its own shared memory reads 96 bytes a
+// clock while TMA writes as much, against the 128 an SM has (without loads the products run at the pipe's rate: 125 us for the op).
 //   MODE 0 ("in"):  A = tokens gathered into sorted order [positions, K]; the expert's matrix is [gate rows | up rows];
 //                   the 256 accumulator columns are 128 gate columns and the 128 up columns of the SAME outputs, and the
 //                   epilogue writes g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(slope * g) * (u + 1).
@@ -20,14 +27,14 @@ using namespace mi::sm100;
 
 namespace {
 
-constexpr int GM = 128, GK = 64, GSTAGES = 4;
+constexpr int GM = 128, GK = 64, GSTAGES = 2;
 constexpr int GA_BYTES = GM * GK * 2, GB_BYTES = 256 * GK * 2, GSTAGE_BYTES = GA_BYTES + GB_BYTES;
 constexpr int GTMEM_COLS = 256;
 
 __device__ __forceinline__ float gated(float g, float u, float limit, float slope) {
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
-    return g / (1.f + expf(-slope * g)) * (u + 1.f);
+    return g * __frcp_rn(1.f + __expf(-slope * g)) * (u + 1.f);
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -35,7 +42,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(256, 2)
 moe_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, __nv_bfloat16* __restrict__ out,
                         int ldo, const int* __restrict__ sorted_pair, const int* __restrict__ tile_expert, int N, int K, float limit,
                         float slope, int* __restrict__ error_word) {
@@ -43,7 +50,7 @@ moe_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_c
     if (e < 0) return;
     extern __shared__ unsigned char gsm_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)gsm_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(base + GSTAGES * GSTAGE_BYTES);        // full[4], empty[4], acc
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + GSTAGES * GSTAGE_BYTES);        // full[], empty[], acc
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * GSTAGES + 1);
     const uint32_t s0 = smem_u32(base), full = smem_u32(bars), empty = smem_u32(bars + GSTAGES), acc_bar = smem_u32(bars + 2 * GSTAGES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -94,18 +101,20 @@ moe_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_c
         umma_commit(acc_bar);                              // and the accumulator is whole
     }
     __syncwarp();
-    // ---------------- epilogue: thread t of warp w owns row 32 w + t (tensor-memory lane 32 w + t)
+    // ---------------- epilogue: thread t of warp w owns row 32 (w % 4) + t (tensor-memory lane of the same number) and the
+    // half w / 4 of the columns
     const bool ok = mbar_wait(acc_bar, 0);
     if (!ok && lane == 0) atomicExch(error_word, 63);
     tc_fence_after();
     if (ok) {
-        const int r = warp * 32 + lane;
+        const int quarter = warp & 3, part = warp >> 2;
+        const int r = quarter * 32 + lane;
         const int pr = sorted_pair[pos0 + r];
-        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
         if (MODE == 0) {
             __nv_bfloat16* orow = out + (size_t)(pos0 + r) * ldo;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 2 * part; c < 2 * part + 2; ++c) {
                 uint32_t g[32], u[32];
                 tmem_ld32(lane_addr + c * 32, g);
                 tmem_ld32(lane_addr + 128 + c * 32, u);
@@ -125,7 +134,7 @@ moe_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_c
         } else {
             __nv_bfloat16* orow = out + (size_t)(pr >= 0 ? pr : 0) * ldo;
 #pragma unroll 1
-            for (int c = 0; c < 8; ++c) {
+            for (int c = 4 * part; c < 4 * part + 4; ++c) {
                 uint32_t o[32];
                 tmem_ld32(lane_addr + c * 32, o);
                 tmem_wait_ld();
@@ -187,7 +196,7 @@ MI_EXPORT int mi_moe_gemm_tcgen05(const void* A, const void* W, int E, void* out
             if (err != cudaSuccess) return (int)err; \
             configured[MODE] = true; \
         } \
-        moe_gemm_tcgen05_kernel<MODE><<<grid, 128, smem, stream>>>(amap, bmap, (__nv_bfloat16*)out, ldo, sorted_pair, tile_expert, N, K, limit, \
+        moe_gemm_tcgen05_kernel<MODE><<<grid, 256, smem, stream>>>(amap, bmap, (__nv_bfloat16*)out, ldo, sorted_pair, tile_expert, N, K, limit, \
                                                                   slope, error_word); } while (0)
     if (mode == 0) GO(0); else GO(1);
 #undef GO

@@ -665,7 +665,7 @@ def test_kernels_against_the_stand_ins(dtype):
         assert close(sa, sb, 1e-4)
     # router and experts
     for T, hid, E, top, groups, F in ((13, 44, 6, 2, (3, 2), 10), (70, 128, 16, 5, (4, 2), 64), (5, 33, 7, 7, None, 9), (40, 64, 8, 1, (8, 1), 64),
-                                      (300, 64, 4, 2, None, 192), (1100, 72, 6, 2, (3, 2), 8), (900, 320, 5, 3, None, 448)):
+                                      (300, 64, 4, 2, None, 192), (1100, 72, 6, 2, (3, 2), 8), (900, 320, 5, 3, None, 576)):
         h, router, corr = rnd(T, hid), rnd(E, hid) * 0.5, f32(E) * 0.2
         ca, wa = ops.route_topk(h.to(dev), router.to(dev), corr.to(dev), top, groups)
         cb, wb = ref.route_topk(h, router, corr, top, groups)
