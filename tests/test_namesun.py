@@ -76,6 +76,11 @@ CONFIGS = {
     "pages": (config(64, 150, [attn(4, 1, 16, 16, block=16, v_mix=True, mlp=moe(4, 4, 16, 2.5, groups=(2, 2))),
                                attn(8, 4, 8, 4, block=32, mlp=moe(8, 2, 8, 1.0, groups=(8, 3), shared=(24, 1.0))),
                                ret(4, 8, 16, [0.6, 0.9, 0.97, 0.999], rot_dims=2, base=1e6, mlp=None)], mult=0.25), 16),
+    # key = value rows of 64 and of 128 entries on pages of 16: in bfloat16 on the GPU these reach the tensor-core prompt and decode
+    # kernels, also in mixed batches; the third layer blends the first one's values
+    "rows64": (config(64, 113, [attn(4, 2, 64, 64, block=24, v_mix=True, mlp=moe(4, 2, 64, 1.2, shared=(64, 1.5))),
+                                ret(2, 16, 8, [0.9, 0.99], rot_dims=8, mlp=dense(48)),
+                                attn(2, 2, 64, 64, block=50, v_mix=True, mlp=dense(72)), attn(2, 1, 128, 128, block=37)], mult=0.6), 16),
 }
 STD = 0.25
 
@@ -567,7 +572,7 @@ def test_cuts_on_gpu(dirs, name, dtype):
 
 @gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["mix", "pages"])
+@pytest.mark.parametrize("name", ["mix", "pages", "rows64"])
 def test_mixed_batches_on_gpu(dirs, name, dtype):
     d, cfg, page = dirs[name]
     check_mixed(lambda pages: engine(d, page, pages, dtype, "cuda:0"), d, cfg["vocab"], page, TOL[dtype])
